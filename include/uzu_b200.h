@@ -484,6 +484,8 @@ typedef struct uzu_dense_linear_args {
     uint32_t reserved0;
     uint64_t gate_bias;            /* optional f32 [n] (with gate): sigmoid(gate[row, col] + gate_bias[col]) */
     uint64_t col_scale;            /* optional f32 [n]: the product is multiplied by col_scale[col] (a per-channel layer scale) */
+    uint64_t row_scale;            /* optional f32 [compact rows]: the product of compact row p is multiplied by row_scale[p] before any
+                                      epilogue (paired unit included): a router weight applied to an expert's input, A . W being linear in A */
 } uzu_dense_linear_args;
 UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
 /* 0, or the code of the first bounded barrier wait that ran out inside a tensor-memory dense product (the kernel gives up and returns) */
@@ -535,6 +537,9 @@ UZU_API void uzu_routed_combine_encode(uzu_command_buffer* cmd, uint64_t pairs, 
 typedef struct uzu_topk_route_args {
     uint64_t logits /* f32 [rows, logits_stride] */, bias /* optional f32 [experts] */, group_offsets, rows_map, pair_pos, pair_weight;
     uint32_t rows, top, experts, logits_stride;
+    uint32_t weight_kind;          /* 0: softmax over the chosen logits; 1: sigmoid of each chosen logit on its own (not renormalised) */
+    uint32_t reserved;
+    uint64_t compact_weight;       /* optional f32 [rows*top]: the same weights in the compact (expert-sorted) order of rows_map */
 } uzu_topk_route_args;
 UZU_API void uzu_topk_route_encode(uzu_command_buffer* cmd, const uzu_topk_route_args* args);
 
@@ -593,11 +598,13 @@ typedef struct uzu_general_delta_args {
 } uzu_general_delta_args;
 UZU_API void uzu_general_delta_encode(uzu_command_buffer* cmd, const uzu_general_delta_args* args);
 
-/* out[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + epsilon) * scales[h*dim + :] * sigmoid(gate[r, h*dim + :]); scales / gate optional */
+/* out[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + epsilon) * scales[h*dim + :] * act(gate[r, h*dim + :]); scales / gate optional;
+ * act = sigmoid (gate_op 0) or silu (gate_op 1) */
 typedef struct uzu_head_norm_gate_args {
     uint64_t x, scales, gate, out;
     uint32_t rows, heads, dim, x_stride, gate_stride, out_stride, normalize;
     float epsilon;
+    uint32_t gate_op, reserved;
 } uzu_head_norm_gate_args;
 UZU_API void uzu_head_norm_gate_encode(uzu_command_buffer* cmd, const uzu_head_norm_gate_args* args);
 
@@ -625,6 +632,62 @@ typedef struct uzu_latent_attention_args {
     uint32_t splits;               /* the causal key range of every query is cut into this many parts, one CTA each (0 / 1 = none) */
 } uzu_latent_attention_args;
 UZU_API void uzu_latent_attention_encode(uzu_command_buffer* cmd, const uzu_latent_attention_args* args);
+
+/* minGRU: a gated recurrence per channel whose gates read only the current token. With z = sigmoid(z_logit) and the candidate
+ * c = u + 1/2 (u >= 0) | sigmoid(u) (u < 0):  S_t = (1 - z_t) S_(t-1) + z_t c_t,  out[t] = S_t * silu(gate[t]) (gate optional).
+ * `rows` tokens of one sequence in one launch; state f32 [n] is read and written back. Long passes cut the rows into chunks whose
+ * (product of 1 - z, sum from zero) pairs are composed in chunk order before every chunk is walked again from its true start state. */
+typedef struct uzu_min_gru_args {
+    uint64_t z_logit, u, gate, state, out;        /* f32 rows with strides (elements); state f32 [n] */
+    uint32_t rows, n, z_stride, u_stride, gate_stride, out_stride;
+} uzu_min_gru_args;
+UZU_API void uzu_min_gru_encode(uzu_command_buffer* cmd, const uzu_min_gru_args* args);
+
+/* Retention: linear attention with one fixed decay per head, no softmax and no denominator. Per head, state S f32 [dim, vdim]:
+ *   S_t = decay[h] * S_(t-1) + (key_scale * k_t) v_t^T,   out[t, h, :] = S_t^T q_t
+ * q, k f32 [rows, heads*dim], v f32 [rows, heads*vdim] (row strides in elements), out f32 [rows, heads*vdim]; `rows` tokens of one
+ * sequence in token order in one launch, the state read from and written back to `state` f32 [heads, dim, vdim]. */
+typedef struct uzu_retention_args {
+    uint64_t q, k, v, decay /* f32 [heads] */, state, out;
+    uint32_t rows, heads, dim, vdim, q_stride, k_stride, v_stride, out_stride;
+    float key_scale;
+    uint32_t reserved;
+} uzu_retention_args;
+UZU_API void uzu_retention_encode(uzu_command_buffer* cmd, const uzu_retention_args* args);
+
+/* Windowed softmax attention, cache side and query side of one pass. Per token row t at position p = prefix + t (prefix read from
+ * dynamic_position when non-zero), per head: optional RMS norm over the head's `dim` channels times q_scales / k_scales [dim] (shared by
+ * all heads), then interleaved-pair rotation of the first 2 * rot_pairs channels by cos / sin rows [positions, rot_pairs]:
+ *   query[t, h, :] = rotate_p(norm(q[t, h, :]))             (f32 [rows, heads*dim])
+ *   keys[p, g, :]  = rotate_p(norm(k[t, g, :]))             (cache_dt [positions, kv_heads*dim])
+ *   values[p, g, :] = rotate_p(v[t, g, :]) over 2 * v_pairs channels by their own cos / sin rows (v_pairs = 0: stored as they are) */
+typedef struct uzu_window_attention_prepare_args {
+    uint64_t q, k, v, q_scales, k_scales, query, keys, values, cosines, sines, v_cosines, v_sines, dynamic_position;
+    uint32_t rows, heads, kv_heads, dim, vdim, rot_pairs, v_pairs, q_stride, k_stride, v_stride, prefix, cache_dt;
+    float epsilon;
+    uint32_t reserved;
+} uzu_window_attention_prepare_args;
+UZU_API void uzu_window_attention_prepare_encode(uzu_command_buffer* cmd, const uzu_window_attention_prepare_args* args);
+
+/* Causal softmax attention of `rows` queries (positions p = prefix + t) over cached keys / values with a sliding window that keeps the
+ * first tokens: key j is visible when j <= p and (p - j < window or j < keep_first); window = 0 means no window. Query head h reads
+ * key / value head h / (heads / kv_heads).
+ *   s = scale * head_temp[h] * query . key;  softcap > 0: s <- softcap * tanh(s / softcap);  weights = softmax over the visible keys
+ *   out[t, h, :] = rotate_(-p)(sum_j weight_j * values[j, g, :])   (the rotation back over 2 * v_pairs channels only when v_pairs > 0)
+ * Scores, weights and sums are f32. bf16 caches with rows >= 64 and dim, vdim multiples of 16 up to 128 run on the tensor pipe with the
+ * query and the weights each as a sum of two bf16 numbers (hi + lo). Few rows: the visible keys of a query are cut into `splits` parts,
+ * one CTA each, merged by the last to finish. */
+typedef struct uzu_window_attention_args {
+    uint64_t query, keys, values, out, dynamic_position;
+    uint64_t head_temp;            /* optional f32 [heads] */
+    uint64_t v_cosines, v_sines;   /* f32 [positions, v_pairs] when v_pairs > 0 */
+    uint64_t partials;             /* scratch f32 [rows, heads, splits, vdim + 2] when splits > 1 */
+    uint64_t tickets;              /* scratch u32 [rows*heads], zero before the first use */
+    uint32_t rows, heads, kv_heads, dim, vdim, prefix, cache_dt, window, keep_first, v_pairs;
+    float scale, softcap;
+    uint32_t splits, reserved;
+} uzu_window_attention_args;
+UZU_API void uzu_window_attention_encode(uzu_command_buffer* cmd, const uzu_window_attention_args* args);
 
 /* ---- Host engine (C++ mirror of the reference's backend-agnostic Rust host code) ---------- *
  * No Rust toolchain exists in the build image, so the layer above the kernels -- Engine /

@@ -136,7 +136,7 @@ DenseLinearArgs = _struct("uzu_dense_linear_args", [
     ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64), ("gate", u64), ("workspace", u64),
     ("m", u32), ("n", u32), ("k", u32), ("lda", u32), ("ldd", u32), ("batch", u32),
     ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("a_op", u32), ("gate_ld", u32), ("pair_rows", u32),
-    ("glu_limit", f32), ("glu_alpha", f32), ("glu_kind", u32), ("reserved0", u32), ("gate_bias", u64), ("col_scale", u64)])
+    ("glu_limit", f32), ("glu_alpha", f32), ("glu_kind", u32), ("reserved0", u32), ("gate_bias", u64), ("col_scale", u64), ("row_scale", u64)])
 
 GroupRmsNormArgs = _struct("uzu_group_rms_norm_args", [
     ("input", u64), ("scales", u64), ("output", u64), ("row_indices", u64),
@@ -155,7 +155,7 @@ GeneralDeltaArgs = _struct("uzu_general_delta_args", [
 HeadNormGateArgs = _struct("uzu_head_norm_gate_args", [
     ("x", u64), ("scales", u64), ("gate", u64), ("out", u64),
     ("rows", u32), ("heads", u32), ("dim", u32), ("x_stride", u32), ("gate_stride", u32), ("out_stride", u32), ("normalize", u32),
-    ("epsilon", f32)])
+    ("epsilon", f32), ("gate_op", u32), ("reserved", u32)])
 
 LatentPrepareArgs = _struct("uzu_latent_prepare_args", [
     ("kv", u64), ("q", u64), ("query", u64), ("cache", u64), ("latent_scales", u64), ("cosines", u64), ("sines", u64),
@@ -169,7 +169,7 @@ LatentAttentionArgs = _struct("uzu_latent_attention_args", [
 
 TopkRouteArgs = _struct("uzu_topk_route_args", [
     ("logits", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64), ("pair_pos", u64), ("pair_weight", u64),
-    ("rows", u32), ("top", u32), ("experts", u32), ("logits_stride", u32)])
+    ("rows", u32), ("top", u32), ("experts", u32), ("logits_stride", u32), ("weight_kind", u32), ("reserved", u32), ("compact_weight", u64)])
 
 RoutedCombineArgs = _struct("uzu_routed_combine_args", [
     ("pairs", u64), ("pair_pos", u64), ("pair_weight", u64), ("gate", u64), ("gate_bias", u64), ("col_scale", u64), ("output", u64),
@@ -187,9 +187,30 @@ SigmoidAttentionArgs = _struct("uzu_sigmoid_attention_args", [
     ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32),
     ("splits", u32), ("chunk_tiles", u32)])
 
+MinGruArgs = _struct("uzu_min_gru_args", [
+    ("z_logit", u64), ("u", u64), ("gate", u64), ("state", u64), ("out", u64),
+    ("rows", u32), ("n", u32), ("z_stride", u32), ("u_stride", u32), ("gate_stride", u32), ("out_stride", u32)])
+
+RetentionArgs = _struct("uzu_retention_args", [
+    ("q", u64), ("k", u64), ("v", u64), ("decay", u64), ("state", u64), ("out", u64),
+    ("rows", u32), ("heads", u32), ("dim", u32), ("vdim", u32), ("q_stride", u32), ("k_stride", u32), ("v_stride", u32), ("out_stride", u32),
+    ("key_scale", f32), ("reserved", u32)])
+
+WindowAttentionPrepareArgs = _struct("uzu_window_attention_prepare_args", [
+    ("q", u64), ("k", u64), ("v", u64), ("q_scales", u64), ("k_scales", u64), ("query", u64), ("keys", u64), ("values", u64),
+    ("cosines", u64), ("sines", u64), ("v_cosines", u64), ("v_sines", u64), ("dynamic_position", u64),
+    ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("rot_pairs", u32), ("v_pairs", u32),
+    ("q_stride", u32), ("k_stride", u32), ("v_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("reserved", u32)])
+
+WindowAttentionArgs = _struct("uzu_window_attention_args", [
+    ("query", u64), ("keys", u64), ("values", u64), ("out", u64), ("dynamic_position", u64), ("head_temp", u64),
+    ("v_cosines", u64), ("v_sines", u64), ("partials", u64), ("tickets", u64),
+    ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("prefix", u32), ("cache_dt", u32), ("window", u32),
+    ("keep_first", u32), ("v_pairs", u32), ("scale", f32), ("softcap", f32), ("splits", u32), ("reserved", u32)])
+
 MAIN_SLOT = 0xFFFFFFFF
 
-ABI_STRUCTS = [TopkRouteArgs, RoutedCombineArgs, SigmoidAttentionPrepareArgs, SigmoidAttentionArgs, DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
+ABI_STRUCTS = [MinGruArgs, RetentionArgs, WindowAttentionPrepareArgs, WindowAttentionArgs, TopkRouteArgs, RoutedCombineArgs, SigmoidAttentionPrepareArgs, SigmoidAttentionArgs, DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
                DeltaNetFusedUpdateArgs, QkNormConfig, AttentionPrepareNormArgs, FusedLinearArgs, RingParams, TrieNode, KvCopy, MatmulArgs, NormalizationArgs, QkvNormArgs, AttentionPrepareArgs, AttentionArgs,
                AttentionTwoPass2Args, KvCacheUpdateArgs, GatedActMulArgs, QuantizedEmbeddingLookupArgs, UnifiedSamplingArgs,
                DeltaNetConvUpdateArgs, DeltaNetUpdateArgs, EngineOptions, SamplingMethod, ModelInfo, TpAllGatherArgs]
@@ -221,7 +242,8 @@ uzu_activation_transform_validate uzu_dense_linear_encode uzu_group_rms_norm_enc
 uzu_unary_f32_encode uzu_residual_add_encode uzu_logit_cap_f32_encode uzu_table_route_encode uzu_routed_combine_encode
 uzu_general_delta_encode uzu_head_norm_gate_encode uzu_latent_prepare_encode uzu_latent_attention_encode
 uzu_silu_glu_encode uzu_topk_route_encode uzu_routed_combine_gated_encode uzu_sigmoid_attention_prepare_encode uzu_sigmoid_attention_encode
-uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs uzu_debug_dense_umma_error""".split()
+uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs uzu_debug_dense_umma_error
+uzu_min_gru_encode uzu_retention_encode uzu_window_attention_prepare_encode uzu_window_attention_encode""".split()
 
 _lib = None
 
@@ -372,6 +394,10 @@ def load() -> C.CDLL:
         "uzu_head_norm_gate_encode": (None, [vp, C.POINTER(HeadNormGateArgs)]),
         "uzu_latent_prepare_encode": (None, [vp, C.POINTER(LatentPrepareArgs)]),
         "uzu_latent_attention_encode": (None, [vp, C.POINTER(LatentAttentionArgs)]),
+        "uzu_min_gru_encode": (None, [vp, C.POINTER(MinGruArgs)]),
+        "uzu_retention_encode": (None, [vp, C.POINTER(RetentionArgs)]),
+        "uzu_window_attention_prepare_encode": (None, [vp, C.POINTER(WindowAttentionPrepareArgs)]),
+        "uzu_window_attention_encode": (None, [vp, C.POINTER(WindowAttentionArgs)]),
         "uzu_engine_slot_acquire": (C.c_int, [vp, C.POINTER(u32)]),
         "uzu_engine_slot_release": (C.c_int, [vp, u32]),
         "uzu_engine_forward_rows": (C.c_int, [vp, u32, C.POINTER(u32), u32, C.POINTER(u32), u32, C.POINTER(C.c_float)]),

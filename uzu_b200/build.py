@@ -43,6 +43,8 @@ SOURCES = {
     "general_delta.cu": [],
     "latent_attention.cu": [],
     "sigmoid_attention.cu": [],
+    "window_attention.cu": [],
+    "linear_recurrence.cu": [],
     "engine.cu": [],
 }
 

@@ -48,6 +48,7 @@ __device__ __forceinline__ float dense_a(const uzu_dense_linear_args& a, float x
 // `row` is the compact row the value belongs to (the gate is indexed like D)
 __device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, float* d, uint32_t z, uint32_t row, uint32_t col, float acc) {
     float v = acc * a.scale;
+    if (a.row_scale) v *= reinterpret_cast<const float*>(a.row_scale)[row];
     if (a.gate) {
         float g = reinterpret_cast<const float*>(a.gate)[(size_t)row * a.gate_ld + (size_t)z * a.d_z_stride + col];
         if (a.gate_bias) g += reinterpret_cast<const float*>(a.gate_bias)[col];
@@ -212,6 +213,9 @@ __global__ void __launch_bounds__(256, RMAX == 1 ? 4 : 2) dense_rows_kernel(cons
     }
     auto finish = [&](uint32_t r, float s, float s2) {
         float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col;
+        if constexpr (PAIR) {
+            if (a.row_scale) { const float rs = reinterpret_cast<const float*>(a.row_scale)[R.begin + r]; s *= rs; s2 *= rs; }
+        }
         if constexpr (PAIR) *d = a.glu_kind == 1 ? s * (1.0f / (1.0f + expf(-s))) * s2 : clamped_glu_value(s, s2, a.glu_limit, a.glu_alpha);
         else dense_store(a, d, z, R.begin + r, col, s);
     };

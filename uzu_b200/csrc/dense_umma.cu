@@ -237,7 +237,7 @@ __global__ void dense_cast_bf16_kernel(const float* a, uint32_t lda, __nv_bfloat
 // of 64, 16-byte aligned operands, and a bf16 workspace of m * k elements from the caller.
 bool dense_umma_applicable(const uzu_dense_linear_args& a) {
     static const bool off = getenv("UZU_DENSE_NO_UMMA") != nullptr;      // A/B runs
-    if (off || !a.workspace || a.weights_dt != UZU_DT_BF16 || a.batch != 1 || a.group_offsets || a.rows_map || a.bias || a.pair_rows) return false;
+    if (off || !a.workspace || a.weights_dt != UZU_DT_BF16 || a.batch != 1 || a.group_offsets || a.rows_map || a.bias || a.pair_rows || a.row_scale) return false;
     if (a.m < 128 || a.k % 64u != 0 || a.n < 64) return false;
     if ((a.a & 15u) || (a.w & 15u) || (a.workspace & 15u) || a.lda % 4u != 0) return false;
     return true;

@@ -354,6 +354,32 @@ struct SigmoidAttentionLayer {  // sigmoid attention: whole-projection q / k nor
     float scale = 1.0f, temp_coef = 0.0f;
 };
 
+struct MinGruLayer {            // minGRU mixer: gates and candidate read only the current token
+    DenseMatrix in;             // rows [update-gate logits | candidate | output gate]
+    DenseMatrix out;
+    Buf in_bias;                // f32 [3 * width] (zeros under the output gate rows)
+    uint32_t width = 0;
+};
+
+struct WindowAttentionLayer {   // softmax attention with a sliding window that keeps the first tokens; q / k head norms, rotated q, k AND values
+    DenseMatrix out;
+    Buf q_norm, k_norm;         // f32 [dim], shared by the heads (absent: no norm)
+    Buf head_temp;              // f32 [heads] (absent: 1)
+    Buf out_bias;               // f32 [width], already times the mixer's share of the sum
+    uint32_t heads = 0, kv_heads = 0, dim = 0, vdim = 0, window = 0, keep_first = 0;
+    uint32_t q_offset = 0, k_offset = 0, v_offset = 0;   // first column of each part in the layer's stacked projection
+    float scale = 1.0f, softcap = 0.0f, share = 1.0f;
+    int rope_index = -1, value_rope_index = -1;          // value_rope_index < 0: values are cached as they are
+};
+
+struct RetentionLayer {         // retention: per head S <- decay S + (k / sqrt(dim)) v^T, out = S^T q; per-head unit RMS, silu gate
+    DenseMatrix out;
+    Buf decay;                  // f32 [heads]
+    uint32_t heads = 0, dim = 0, vdim = 0;
+    uint32_t q_offset = 0, k_offset = 0, v_offset = 0, gate_offset = 0;
+    float share = 1.0f;
+};
+
 struct SublayerGate {           // y * scale[c] * sigmoid(gate_logit[c] + bias[c]); the gate logits are extra rows of the sublayer's stacked input projection
     bool present = false;
     Buf scale, bias;            // f32 [width]
@@ -366,12 +392,15 @@ struct GatedMlp {               // feed-forward: dense or routed experts; the un
     DenseMatrix gate_up /* experts x [2f, W]: gate rows then up rows; ReluSquared: [f (+ W gate logits), W] */, down /* experts x [W, f] */;
     DenseMatrix router;         // RoutedExperts: rows [router logits | sublayer gate]
     Buf table;                  // TableExperts: i32 [vocab, top]
-    Buf router_bias;            // RoutedExperts: f32 [experts]
+    Buf router_bias;            // RoutedExperts: f32 [experts] (optional)
     uint32_t f = 0, experts = 1, top = 1;
     float limit = 0.0f;
+    bool sigmoid_weights = false;   // RoutedExperts: a chosen expert's weight is the sigmoid of its own logit (default: softmax over the chosen)
+    bool weight_on_input = false;   // RoutedExperts: the weight multiplies the expert's input, not its output
 };
 
-enum MixerKind : uint32_t { MixAttention = 0, MixDeltaNet = 1, MixGeneralDelta = 2, MixLatentAttention = 3, MixSigmoidAttention = 4 };
+enum MixerKind : uint32_t { MixAttention = 0, MixDeltaNet = 1, MixGeneralDelta = 2, MixLatentAttention = 3, MixSigmoidAttention = 4,
+                           MixMinGru = 5, MixWindowAttention = 6, MixRetention = 7, MixSideBySide = 8 /* window attention + retention, summed */ };
 
 struct Layer {
     bool is_attention = true;   // the mixer keeps a per-token cache whose length advances with the context (MixAttention, MixLatentAttention)
@@ -382,6 +411,14 @@ struct Layer {
     GeneralDeltaLayer gd;
     LatentAttentionLayer la;
     SigmoidAttentionLayer sa;
+    MinGruLayer mg;
+    WindowAttentionLayer wa;
+    RetentionLayer rt;
+    DenseMatrix side_in;        // MixWindowAttention / MixRetention / MixSideBySide: the stacked input projection of the layer's mixers
+    Buf side_in_bias;           // f32 [side_in.rows] when any part has biases
+    bool sequential = false;    // parallel-block engine: the feed-forward reads the residual AFTER the mixer's sum, through its own norm
+    bool has_window_attention() const { return kind == MixWindowAttention || kind == MixSideBySide; }
+    bool has_retention() const { return kind == MixRetention || kind == MixSideBySide; }
     SublayerGate mix_gate, mlp_gate;
     GatedMlp gmlp;
     Linear up, down;
@@ -470,6 +507,7 @@ struct uzu_engine {
     Buf pb_final_norm;
     struct PbScratch {
         Buf normed2, proj2, pair_weight, attn_tickets;   // second normed copy, the feed-forward's router / gate logits, router weights, split tickets
+        Buf pair_weight_compact;                         // router weights in the expert-sorted order of the pair list
         Buf resid, normed, operand_bf16, proj, lat, wide, lat_wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;
@@ -727,6 +765,7 @@ static void rope_tables(const RopeCfg& c, uint32_t count, float* cosines, float*
 
 static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std::string& dir);
 static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string& dir);
+static void load_vugipel_model(uzu_engine* e, const Json& cfg, const std::string& dir);
 static void load_language_model_config(uzu_engine* e, const Json& cfg, const std::string& dir);
 
 // Model registry: config.json names its family, either by the reference's type tag or by an "architecture" string.
@@ -739,6 +778,7 @@ static const ModelFamily kModelFamilies[] = {
     {"LanguageModelConfig", [](const Json& c) { const Json* t = c.get("type"); return t && t->str == "LanguageModelConfig"; }, load_language_model_config},
     {"Punilix", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Punilix"; }, load_parallel_block_model},
     {"Gamanex", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Gamanex"; }, load_gamanex_model},
+    {"Vugipel", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Vugipel"; }, load_vugipel_model},
 };
 
 static void load_model(uzu_engine* e, const std::string& dir) {
@@ -959,6 +999,28 @@ static void alloc_layer_state(uzu_engine* e, const Layer& L, LayerState& S, uint
             S.ssm_bytes = (size_t)L.gd.heads * L.gd.dim * L.gd.dim * 4;
             fixed(S.ssm_state, S.ssm_bytes);
             S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
+            break;
+        }
+        case MixMinGru: {            // f32 [width]
+            S.ssm_bytes = (size_t)L.mg.width * 4;
+            fixed(S.ssm_state, S.ssm_bytes);
+            S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
+            break;
+        }
+        case MixWindowAttention:
+        case MixRetention:
+        case MixSideBySide: {        // a layer may hold both: a per-token cache for the attention and an f32 [heads, dim, vdim] state for the retention
+            if (L.has_window_attention()) {
+                const size_t kb = (size_t)L.wa.kv_heads * L.wa.dim * storage_size(e->store_dt), vb = (size_t)L.wa.kv_heads * L.wa.vdim * storage_size(e->store_dt);
+                S.row_bytes = std::max(kb, vb);     // both buffers reserve the larger row's range: their pages are mapped by one page list
+                paged(S.k_sparse, S.k_dense, S.keys, (size_t)rows_total * S.row_bytes);
+                paged(S.v_sparse, S.v_dense, S.values, (size_t)rows_total * S.row_bytes);
+            }
+            if (L.has_retention()) {
+                S.ssm_bytes = (size_t)L.rt.heads * L.rt.dim * L.rt.vdim * 4;
+                fixed(S.ssm_state, S.ssm_bytes);
+                S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
+            }
             break;
         }
         default: throw std::runtime_error("unknown mixer kind");
@@ -2372,9 +2434,8 @@ uzu_status uzu_engine_restore(uzu_engine* e) {
             if (S.ssm_state.b) {
                 if (S.conv_state.b) cudaMemcpyAsync((void*)S.conv_state.ptr(), (void*)S.conv_snapshot.ptr(), S.conv_bytes, cudaMemcpyDeviceToDevice, s);
                 cudaMemcpyAsync((void*)S.ssm_state.ptr(), (void*)S.ssm_snapshot.ptr(), S.ssm_bytes, cudaMemcpyDeviceToDevice, s);
-            } else {
-                S.length = e->snapshot_context;   // KV rows beyond the snapshot are simply overwritten
             }
+            if (e->layers[i].is_attention) S.length = e->snapshot_context;   // KV rows beyond the snapshot are simply overwritten (a layer may hold both)
         }
         cudaMemcpyAsync((void*)e->token_ids.ptr(), (void*)e->snapshot_token.ptr(), 4, cudaMemcpyDeviceToDevice, s);
         e->context_length = e->snapshot_context;

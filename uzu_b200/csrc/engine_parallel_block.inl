@@ -1,9 +1,10 @@
-// Parallel-block families (Punilix, Gamanex) inside the host engine: configuration, weights, scratch and the encoding of one pass.
+// Parallel-block families (Punilix, Gamanex) and the sequential-sublayer family Vugipel inside the host engine: configuration, weights, scratch and the encoding of one pass.
 // Included by engine.cu; the pass driver, the state / cache manager, sampling, CUDA-graph decode and the sequence slots are the engine's own.
 //
 //   x = embed[token]                                                      (f32 residual stream)
 //   Punilix layer:  h = group_rms(x);  x <- x + mixer(h) + mlp(h)         (one norm feeds both sublayers)
 //   Gamanex layer:  h1 = rms(x) n1, h2 = rms(x) n2;  x <- x + ls1 sigmoid(G1 h1 + b1) mixer(h1) + ls2 sigmoid(G2 h2 + b2) mlp(h2)
+//   Vugipel layer:  x <- x + mixer(rms(x) (1 + n1));  x <- x + mlp(rms(x) (1 + n2))     (Layer::sequential)
 //   logits = cap * tanh(head . group_rms(x) / cap)   |   logit_scale * head . rms(x)
 //
 // Both are described by the same Layer fields (a second norm, sublayer gates and a logit scale are optional parts) and encoded by the same
@@ -409,6 +410,200 @@ static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string
     e->info.state_bytes_per_token = 0;
 }
 
+// Vugipel: sequential pre-norm layers (x <- x + mixer(n1(x)), then x <- x + ff(n2(x))) whose norm weights are stored as distances from
+// one; mixers: minGRU, or window attention and retention side by side (both read the same normed input, their outputs are summed with
+// fixed shares); feed-forward: routed silu-gated experts whose sigmoid router weight multiplies the expert's INPUT, or none.
+// config.json: "width", "vocab", "norm": {"eps"}, "layers": [{"type": "mingru", "mixer": {"width"}} | {"type": "parallel", "mixer":
+// {"left": {"heads", "kv_heads", "dim", "vdim", "scale", "softcap", "rot": {"base", "dims"}, "mask": {"size", "keep_first"}}, "left_scale",
+// "right": {"heads", "dim", "vdim", "decay": [..]}, "right_scale"}}, each with "mlp": null | {"kind": "moe", "expert": {"ff"}, "router":
+// {"experts", "top"}}]. Tensors: l<i>.norm1/2, l<i>.mix.{z,z.b,x,x.b,g,o} | l<i>.mix.left.{q,k,v,o (+ .b), q.norm, k.norm, temp},
+// l<i>.mix.right.{q,k,v,g,o}; l<i>.mlp.{router, e<x>.{gate,up,down}}.
+static void load_vugipel_model(uzu_engine* e, const Json& cfg, const std::string& dir) {
+    if (e->opts.tp_size > 1) throw std::runtime_error("tensor parallelism is not built for the parallel-block families");
+    e->parallel_block = true;
+    e->store_dt = e->opts.storage_f32 ? UZU_DT_F32 : UZU_DT_BF16;
+    const uint32_t W = e->model_dim = cfg_u32(cfg, "width");
+    const uint32_t V = e->vocab = cfg_u32(cfg, "vocab");
+    e->norm_eps = (float)cfg.at("norm").at("eps").number();
+    e->norm_groups = 1;
+    ParameterLoader pl(dir + "/model.safetensors");
+    // a norm weight w stands for the factor 1 + w (formed once, in f32)
+    auto offset_norm = [&](const std::string& name) {
+        HostTensor t = read_floats(pl, name, {W});
+        for (float& v : t.v) v = 1.0f + v;
+        return upload_f32(e, t.v);
+    };
+    auto rope = [&](float base, uint32_t dims) {
+        RopeCfg rc;
+        rc.kind = 3;
+        rc.base = base;
+        rc.head_dim = dims;
+        rc.max_sequence_length = 0xFFFFFFFFu;
+        for (size_t r = 0; r < e->ropes.size(); ++r)
+            if (e->ropes[r] == rc) return (int)r;
+        e->ropes.push_back(rc);
+        return (int)e->ropes.size() - 1;
+    };
+    e->pb_embed = upload_matrix(e, read_floats(pl, "embed", {V, W}).v, V, W);
+    e->pb_head = upload_matrix(e, read_floats(pl, "head", {V, W}).v, V, W);
+    e->pb_final_norm = offset_norm("final.norm");
+    uint64_t wbytes = e->pb_head.bytes, kvb = 0, stb = 0;
+    uint32_t n_cache = 0, n_rec = 0;
+    const auto& lcs = cfg.at("layers").arr;
+    e->layers.resize(lcs.size());
+    for (size_t i = 0; i < lcs.size(); ++i) {
+        const Json& lc = lcs[i];
+        Layer& L = e->layers[i];
+        const std::string p = "l" + std::to_string(i) + ".";
+        L.sequential = true;
+        L.pre_mixer.present = true;
+        L.pre_mixer.n = W;
+        L.pre_mixer.cfg.epsilon = e->norm_eps;
+        L.pre_mixer.scales = offset_norm(p + "norm1");
+        const std::string type = lc.at("type").str;
+        const Json& mc = lc.at("mixer");
+        if (type == "mingru") {
+            L.kind = MixMinGru;
+            L.is_attention = false;
+            MinGruLayer& G = L.mg;
+            G.width = cfg_u32(mc, "width");
+            if (G.width == 0) throw std::runtime_error(p + "mix: width must be positive");
+            std::vector<float> in, bias;
+            append(in, read_floats(pl, p + "mix.z", {G.width, W}));
+            append(in, read_floats(pl, p + "mix.x", {G.width, W}));
+            append(in, read_floats(pl, p + "mix.g", {G.width, W}));
+            append(bias, read_floats(pl, p + "mix.z.b", {G.width}));
+            append(bias, read_floats(pl, p + "mix.x.b", {G.width}));
+            bias.resize((size_t)3 * G.width, 0.0f);
+            G.in = upload_matrix(e, in, 3 * G.width, W);
+            G.in_bias = upload_f32(e, bias);
+            G.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, G.width}).v, W, G.width);
+            wbytes += G.in.bytes + G.out.bytes;
+            stb += 2ull * G.width * 4;
+            n_rec++;
+        } else if (type == "parallel") {
+            L.kind = MixSideBySide;
+            L.is_attention = true;
+            WindowAttentionLayer& A = L.wa;
+            RetentionLayer& R = L.rt;
+            const Json& lj = mc.at("left");
+            const Json& rj = mc.at("right");
+            A.heads = cfg_u32(lj, "heads");
+            A.kv_heads = cfg_u32(lj, "kv_heads");
+            A.dim = cfg_u32(lj, "dim");
+            A.vdim = cfg_u32(lj, "vdim");
+            A.scale = (float)lj.at("scale").number();
+            A.share = (float)mc.at("left_scale").number();
+            if (const Json* sc = lj.get("softcap")) { if (!sc->is_null()) A.softcap = (float)sc->number(); }
+            if (const Json* mk = lj.get("mask")) {
+                if (!mk->is_null()) { A.window = cfg_u32(*mk, "size"); A.keep_first = cfg_u32(*mk, "keep_first"); }
+            }
+            if (A.heads == 0 || A.kv_heads == 0 || A.heads % A.kv_heads || A.dim == 0 || A.vdim == 0 || A.dim > 512 || A.vdim > 512)
+                throw std::runtime_error(p + "mix.left: kv_heads must divide heads, head sizes must be in 1..512");
+            if (A.softcap < 0.0f) throw std::runtime_error(p + "mix.left: softcap must not be negative");
+            if (const Json* rot = lj.get("rot")) {
+                if (!rot->is_null()) {
+                    const float base = (float)rot->at("base").number();
+                    const uint32_t dims = cfg_u32(*rot, "dims");
+                    if (dims % 2 || dims > A.dim || A.vdim % 2) throw std::runtime_error(p + "mix.left: rot.dims must be even and at most dim, vdim must be even");
+                    if (dims) A.rope_index = rope(base, dims);
+                    A.value_rope_index = rope(base, A.vdim);         // values turn over all their channels, with frequencies of their own
+                }
+            }
+            R.heads = cfg_u32(rj, "heads");
+            R.dim = cfg_u32(rj, "dim");
+            R.vdim = cfg_u32(rj, "vdim");
+            R.share = (float)mc.at("right_scale").number();
+            if (R.heads == 0 || R.dim == 0 || R.dim > 1024 || R.vdim == 0) throw std::runtime_error(p + "mix.right: heads / vdim must be positive, dim in 1..1024");
+            {
+                const auto& dj = rj.at("decay").arr;
+                if (dj.size() != R.heads) throw std::runtime_error(p + "mix.right: one decay per head is expected");
+                std::vector<float> d;
+                for (const Json& x : dj) d.push_back((float)x.number());
+                R.decay = upload_f32(e, d);
+            }
+            const uint32_t lq = A.heads * A.dim, lk = A.kv_heads * A.dim, lv = A.kv_heads * A.vdim, rq = R.heads * R.dim, rv = R.heads * R.vdim;
+            const std::string l = p + "mix.left.", r = p + "mix.right.";
+            std::vector<float> in, bias;
+            append(in, read_floats(pl, l + "q", {lq, W}));
+            append(in, read_floats(pl, l + "k", {lk, W}));
+            append(in, read_floats(pl, l + "v", {lv, W}));
+            append(in, read_floats(pl, r + "q", {rq, W}));
+            append(in, read_floats(pl, r + "k", {rq, W}));
+            append(in, read_floats(pl, r + "v", {rv, W}));
+            append(in, read_floats(pl, r + "g", {rv, W}));
+            append(bias, read_floats(pl, l + "q.b", {lq}));
+            append(bias, read_floats(pl, l + "k.b", {lk}));
+            append(bias, read_floats(pl, l + "v.b", {lv}));
+            A.q_offset = 0; A.k_offset = lq; A.v_offset = lq + lk;
+            R.q_offset = lq + lk + lv; R.k_offset = R.q_offset + rq; R.v_offset = R.k_offset + rq; R.gate_offset = R.v_offset + rv;
+            const uint32_t rows = R.gate_offset + rv;
+            bias.resize(rows, 0.0f);
+            L.side_in = upload_matrix(e, in, rows, W);
+            L.side_in_bias = upload_f32(e, bias);
+            A.q_norm = upload_f32(e, read_floats(pl, l + "q.norm", {A.dim}).v);
+            A.k_norm = upload_f32(e, read_floats(pl, l + "k.norm", {A.dim}).v);
+            A.head_temp = upload_f32(e, read_floats(pl, l + "temp", {A.heads}).v);
+            A.out = upload_matrix(e, read_floats(pl, l + "o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
+            {
+                HostTensor ob = read_floats(pl, l + "o.b", {W});
+                for (float& v : ob.v) v *= A.share;
+                A.out_bias = upload_f32(e, ob.v);
+            }
+            R.out = upload_matrix(e, read_floats(pl, r + "o", {W, rv}).v, W, rv);
+            wbytes += L.side_in.bytes + A.out.bytes + R.out.bytes;
+            kvb += (uint64_t)(lk + lv) * storage_size(e->store_dt);
+            stb += 2ull * R.heads * R.dim * R.vdim * 4;
+            n_cache++;
+            n_rec++;
+        } else {
+            throw std::runtime_error("layer type '" + type + "' is not known to the Vugipel family");
+        }
+        GatedMlp& M = L.gmlp;
+        const Json* ml = lc.get("mlp");
+        if (!ml || ml->is_null()) {
+            if (pl.tensors.count(p + "norm2")) read_floats(pl, p + "norm2", {W});       // a norm without a sublayer: checked, not used
+            continue;
+        }
+        L.pre_mlp.present = true;
+        L.pre_mlp.n = W;
+        L.pre_mlp.cfg.epsilon = e->norm_eps;
+        L.pre_mlp.scales = offset_norm(p + "norm2");
+        const std::string kind = ml->at("kind").str;
+        if (kind != "moe") throw std::runtime_error("mlp kind '" + kind + "' is not known to the Vugipel family");
+        M.kind = GatedMlp::RoutedExperts;
+        M.unit = GatedMlp::SiluGlu;
+        M.sigmoid_weights = true;
+        M.weight_on_input = true;
+        M.f = cfg_u32(ml->at("expert"), "ff");
+        M.experts = cfg_u32(ml->at("router"), "experts");
+        M.top = cfg_u32(ml->at("router"), "top");
+        if (M.f == 0 || M.experts == 0 || M.top == 0 || M.top > M.experts || M.experts > 8192 || (uint64_t)MAX_ROWS * M.top * 2 > 40000)
+            throw std::runtime_error(p + "mlp: bad expert / top counts");
+        std::vector<float> gu, dn;
+        M.router = upload_matrix(e, read_floats(pl, p + "mlp.router", {M.experts, W}).v, M.experts, W);
+        for (uint32_t x = 0; x < M.experts; ++x) {
+            const std::string q = p + "mlp.e" + std::to_string(x) + ".";
+            append(gu, read_floats(pl, q + "gate", {M.f, W}));
+            append(gu, read_floats(pl, q + "up", {M.f, W}));
+            append(dn, read_floats(pl, q + "down", {W, M.f}));
+        }
+        M.gate_up = upload_matrix(e, gu, 2 * M.f, W, M.experts);
+        M.down = upload_matrix(e, dn, W, M.f, M.experts);
+        wbytes += M.router.bytes + (M.gate_up.bytes + M.down.bytes) / M.experts * M.top;
+    }
+    pl.assert_all_validated();
+    e->info.model_dim = W;
+    e->info.hidden_dim = 0;
+    e->info.vocab_size = V;
+    e->info.num_layers = (uint32_t)e->layers.size();
+    e->info.num_attention_layers = n_cache;
+    e->info.num_delta_net_layers = n_rec;
+    e->info.weight_bytes_per_token = wbytes;
+    e->info.kv_bytes_per_token_per_ctx = kvb;
+    e->info.state_bytes_per_token = stb;
+}
+
 constexpr uint32_t kPromptChunks = 8;  // most key chunks of a row tile of a sigmoid-attention prompt pass
 constexpr uint32_t kSplitRows = 256;   // query rows x key splits of one latent-attention launch that leaves partial softmax states
 
@@ -430,6 +625,25 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             if (e->store_dt == UZU_DT_BF16) prompt_partial = std::max(prompt_partial, A.heads * A.vdim);    // chunked tensor-pipe prompt passes
             tickets = std::max(tickets, A.heads);
             kmax = std::max(kmax, A.heads * A.vdim);
+        } else if (L.kind == MixMinGru) {
+            proj = std::max(proj, L.mg.in.rows);
+            gated = std::max(gated, L.mg.width);
+            kmax = std::max(kmax, L.mg.width);
+        } else if (L.has_window_attention() || L.has_retention()) {
+            proj = std::max(proj, L.side_in.rows);
+            if (L.has_window_attention()) {
+                const WindowAttentionLayer& A = L.wa;
+                query = std::max(query, A.heads * A.dim);
+                mixed = std::max(mixed, A.heads * A.vdim);
+                partial = std::max(partial, A.heads * (A.vdim + 2));
+                tickets = std::max(tickets, A.heads);
+                kmax = std::max(kmax, A.heads * A.vdim);
+            }
+            if (L.has_retention()) {
+                wide = std::max(wide, L.rt.heads * L.rt.vdim);
+                gated = std::max(gated, L.rt.heads * L.rt.vdim);
+                kmax = std::max(kmax, L.rt.heads * L.rt.vdim);
+            }
         } else if (L.kind == MixGeneralDelta) {
             const uint32_t HD = L.gd.heads * L.gd.dim;
             proj = std::max(proj, L.gd.in.rows);
@@ -467,6 +681,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     if (second_norm) P.normed2 = dev(R * W * 4);
     P.proj2 = dev(R * proj2 * 4);
     P.pair_weight = dev(R * top * 4);
+    P.pair_weight_compact = dev(R * top * 4);
     P.attn_tickets = dev((size_t)kSplitRows * tickets * 4);
     cudaMemset((void*)P.attn_tickets.ptr(), 0, (size_t)kSplitRows * tickets * 4);
     P.operand_bf16 = dev(R * kmax * 2);     // bf16 copy of a prompt pass's activation rows for the tensor-memory products
@@ -553,6 +768,93 @@ static void encode_sigmoid_attention(uzu_engine* e, uzu_command_buffer* cmd, con
     }
     uzu_sigmoid_attention_encode(cmd, &aa);
     encode_into_residual(e, cmd, A.out, P.mixed.ptr(), A.heads * A.vdim, m, &L.mix_gate, P.proj.ptr(), ld);
+}
+
+// h [m, W] -> minGRU: one stacked projection [gate logits | candidate | output gate] with its biases, the scan over the pass with the
+// state carried in S, and the output projection that adds into the residual stream
+static void encode_min_gru(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+    const MinGruLayer& G = L.mg;
+    auto& P = e->pb;
+    const uint32_t m = pc.m, ld = G.in.rows;
+    {
+        uzu_dense_linear_args x = dense_args(e, G.in, P.normed.ptr(), m, P.proj.ptr());
+        x.lda = e->model_dim; x.bias = G.in_bias.ptr();
+        uzu_dense_linear_encode(cmd, &x);
+    }
+    uzu_min_gru_args ga{};
+    ga.z_logit = P.proj.ptr(); ga.u = P.proj.ptr() + (uint64_t)G.width * 4; ga.gate = P.proj.ptr() + (uint64_t)2 * G.width * 4;
+    ga.state = S.ssm_state.ptr(); ga.out = P.gated_mix.ptr();
+    ga.rows = m; ga.n = G.width; ga.z_stride = ga.u_stride = ga.gate_stride = ld; ga.out_stride = G.width;
+    uzu_min_gru_encode(cmd, &ga);
+    encode_into_residual(e, cmd, G.out, P.gated_mix.ptr(), G.width, m);
+}
+
+// Window attention and / or retention reading the same normed input through ONE stacked projection; each output projection adds its share
+// into the residual stream.
+static void encode_side_by_side(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+    auto& P = e->pb;
+    const uint32_t m = pc.m, ld = L.side_in.rows;
+    const uint64_t dyn = pc.dynamic ? e->decode_state.ptr() : 0;
+    {
+        uzu_dense_linear_args x = dense_args(e, L.side_in, P.normed.ptr(), m, P.proj.ptr());
+        x.lda = e->model_dim;
+        if (L.side_in_bias.b) x.bias = L.side_in_bias.ptr();
+        uzu_dense_linear_encode(cmd, &x);
+    }
+    if (L.has_window_attention()) {
+        const WindowAttentionLayer& A = L.wa;
+        const uint64_t vcos = A.value_rope_index >= 0 ? e->rope_cos[A.value_rope_index].ptr() : 0, vsin = A.value_rope_index >= 0 ? e->rope_sin[A.value_rope_index].ptr() : 0;
+        const uint32_t v_pairs = A.value_rope_index >= 0 ? A.vdim / 2 : 0;
+        uzu_window_attention_prepare_args pa{};
+        pa.q = P.proj.ptr() + (uint64_t)A.q_offset * 4; pa.k = P.proj.ptr() + (uint64_t)A.k_offset * 4; pa.v = P.proj.ptr() + (uint64_t)A.v_offset * 4;
+        pa.q_scales = A.q_norm.ptr(); pa.k_scales = A.k_norm.ptr(); pa.query = P.query.ptr(); pa.keys = S.keys; pa.values = S.values;
+        if (A.rope_index >= 0) {
+            pa.cosines = e->rope_cos[A.rope_index].ptr(); pa.sines = e->rope_sin[A.rope_index].ptr();
+            pa.rot_pairs = e->ropes[A.rope_index].head_dim / 2;
+        }
+        pa.v_cosines = vcos; pa.v_sines = vsin; pa.v_pairs = v_pairs; pa.dynamic_position = dyn;
+        pa.rows = m; pa.heads = A.heads; pa.kv_heads = A.kv_heads; pa.dim = A.dim; pa.vdim = A.vdim;
+        pa.q_stride = pa.k_stride = pa.v_stride = ld; pa.prefix = S.length; pa.cache_dt = e->store_dt; pa.epsilon = e->norm_eps;
+        uzu_window_attention_prepare_encode(cmd, &pa);
+        uzu_window_attention_args aa{};
+        aa.query = P.query.ptr(); aa.keys = S.keys; aa.values = S.values; aa.out = P.mixed.ptr(); aa.dynamic_position = dyn;
+        aa.head_temp = A.head_temp.ptr(); aa.v_cosines = vcos; aa.v_sines = vsin; aa.v_pairs = v_pairs;
+        aa.rows = m; aa.heads = A.heads; aa.kv_heads = A.kv_heads; aa.dim = A.dim; aa.vdim = A.vdim; aa.prefix = S.length; aa.cache_dt = e->store_dt;
+        aa.window = A.window; aa.keep_first = A.keep_first; aa.scale = A.scale; aa.softcap = A.softcap;
+        {   // few query rows: cut the visible keys (in tiles of 16) so that about eight small CTAs per SM run (the captured step sizes the
+            // cut for the largest context its graph serves; a window bounds it)
+            uint32_t bound = pc.dynamic ? attention_bucket(S.length + m) : S.length + m;
+            if (A.window) bound = std::min(bound, A.window + A.keep_first);
+            const uint32_t tiles = (bound + 15) / 16;
+            const uint32_t want = std::max(1u, 8u * (uint32_t)e->ctx->sm_count / std::max(1u, m * A.heads));
+            aa.splits = std::min({tiles, want, kSplitRows / std::max(1u, m), 128u});
+            aa.partials = P.attn_partial.ptr(); aa.tickets = P.attn_tickets.ptr();
+            if (aa.splits < 2 || m > kSplitRows) aa.splits = 1;
+        }
+        uzu_window_attention_encode(cmd, &aa);
+        uzu_dense_linear_args x = dense_args(e, A.out, P.mixed.ptr(), m, P.resid.ptr());
+        x.lda = A.heads * A.vdim; x.accumulate = 1; x.scale = A.share;
+        if (A.out_bias.b) x.bias = A.out_bias.ptr();
+        uzu_dense_linear_encode(cmd, &x);
+    }
+    if (L.has_retention()) {
+        const RetentionLayer& R = L.rt;
+        const uint32_t rv = R.heads * R.vdim;
+        uzu_retention_args ra{};
+        ra.q = P.proj.ptr() + (uint64_t)R.q_offset * 4; ra.k = P.proj.ptr() + (uint64_t)R.k_offset * 4; ra.v = P.proj.ptr() + (uint64_t)R.v_offset * 4;
+        ra.decay = R.decay.ptr(); ra.state = S.ssm_state.ptr(); ra.out = P.wide.ptr();
+        ra.rows = m; ra.heads = R.heads; ra.dim = R.dim; ra.vdim = R.vdim; ra.q_stride = ra.k_stride = ra.v_stride = ld; ra.out_stride = rv;
+        ra.key_scale = 1.0f / sqrtf((float)R.dim);
+        uzu_retention_encode(cmd, &ra);
+        uzu_head_norm_gate_args na{};
+        na.x = P.wide.ptr(); na.gate = P.proj.ptr() + (uint64_t)R.gate_offset * 4; na.out = P.gated_mix.ptr();
+        na.rows = m; na.heads = R.heads; na.dim = R.vdim; na.x_stride = rv; na.gate_stride = ld; na.out_stride = rv; na.normalize = 1;
+        na.epsilon = e->norm_eps; na.gate_op = 1;
+        uzu_head_norm_gate_encode(cmd, &na);
+        uzu_dense_linear_args x = dense_args(e, R.out, P.gated_mix.ptr(), m, P.resid.ptr());
+        x.lda = rv; x.accumulate = 1; x.scale = R.share;
+        uzu_dense_linear_encode(cmd, &x);
+    }
 }
 
 // h [m, W] -> the mixer's output is added to the residual stream
@@ -649,6 +951,7 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
     auto gate_up_args = [&]() {
         uzu_dense_linear_args up = dense_args(e, M.gate_up, h, m, paired ? P.act.ptr() : P.gate_up.ptr());
         up.lda = W;
+        if (M.weight_on_input) up.row_scale = P.pair_weight_compact.ptr();      // expert(w h): the first product is linear in its input
         if (paired) { up.n = M.f; up.ldd = M.f; up.pair_rows = M.f; up.glu_limit = M.limit; up.glu_alpha = kGateSlope; up.glu_kind = M.unit == GatedMlp::SiluGlu ? 1 : 0; }
         return up;
     };
@@ -676,6 +979,9 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
         ra.logits = P.proj2.ptr(); ra.bias = M.router_bias.ptr(); ra.group_offsets = P.group_offsets.ptr(); ra.rows_map = P.rows_map.ptr();
         ra.pair_pos = P.pair_pos.ptr(); ra.pair_weight = P.pair_weight.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts;
         ra.logits_stride = M.router.rows;
+        ra.weight_kind = M.sigmoid_weights ? 1 : 0;
+        if (M.weight_on_input) ra.compact_weight = P.pair_weight_compact.ptr();
+        if (!M.router_bias.b) ra.bias = 0;
         uzu_topk_route_encode(cmd, &ra);
     } else {
         uzu_table_route_args ra{};
@@ -694,7 +1000,7 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
     uzu_dense_linear_encode(cmd, &dn);
     uzu_routed_combine_args ca{};
     ca.pairs = P.pair_out.ptr(); ca.pair_pos = P.pair_pos.ptr(); ca.output = P.resid.ptr(); ca.rows = m; ca.top = M.top; ca.n = W; ca.accumulate = 1;
-    if (M.kind == GatedMlp::RoutedExperts) { ca.pair_weight = P.pair_weight.ptr(); ca.weight = 1.0f; }
+    if (M.kind == GatedMlp::RoutedExperts) { ca.pair_weight = M.weight_on_input ? 0 : P.pair_weight.ptr(); ca.weight = 1.0f; }
     else ca.weight = 1.0f / (float)M.top;
     if (L.mlp_gate.present) {
         if (L.mlp_gate.bias.b) { ca.gate = P.proj2.ptr() + (uint64_t)L.mlp_gate.offset * 4; ca.gate_ld = M.router.rows; ca.gate_bias = L.mlp_gate.bias.ptr(); }
@@ -718,12 +1024,19 @@ static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd
         uzu_group_rms_norm_args na{};
         na.input = P.resid.ptr(); na.scales = L.pre_mixer.scales.ptr(); na.output = P.normed.ptr();
         na.rows = m; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
-        const bool second = L.pre_mlp.present && L.gmlp.kind != GatedMlp::None;      // the feed-forward norms the same x with its own weights
+        const bool second = !L.sequential && L.pre_mlp.present && L.gmlp.kind != GatedMlp::None;      // the feed-forward norms the same x with its own weights
         if (second) { na.scales2 = L.pre_mlp.scales.ptr(); na.output2 = P.normed2.ptr(); }
         uzu_group_rms_norm_encode(cmd, &na);
         if (L.kind == MixGeneralDelta) encode_general_delta(e, cmd, L, S, pc);
         else if (L.kind == MixSigmoidAttention) encode_sigmoid_attention(e, cmd, L, S, pc);
+        else if (L.kind == MixMinGru) encode_min_gru(e, cmd, L, S, pc);
+        else if (L.has_window_attention() || L.has_retention()) encode_side_by_side(e, cmd, L, S, pc);
         else encode_latent_attention(e, cmd, L, S, pc);
+        if (L.sequential && L.gmlp.kind != GatedMlp::None) {     // the feed-forward norms the residual the mixer has just added to
+            uzu_group_rms_norm_args nb = na;
+            nb.scales = L.pre_mlp.scales.ptr(); nb.scales2 = 0; nb.output2 = 0;
+            uzu_group_rms_norm_encode(cmd, &nb);
+        }
         if (L.gmlp.kind != GatedMlp::None) encode_gated_mlp(e, cmd, L, pc, second ? P.normed2.ptr() : P.normed.ptr());
         if (dump) uzu_command_buffer_encode_copy(cmd, P.resid.ptr(), P.layer_dump.ptr() + (uint64_t)i * MAX_ROWS * W * 4, (size_t)m * W * 4);
     }

@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const uzu_head_norm
     for (uint32_t i = lane; i < a.dim; i += 32) {
         float v = x[i] * inv;
         if (sc) v *= sc[i];
-        if (gate) v *= 1.0f / (1.0f + expf(-gate[i]));
+        if (gate) v *= a.gate_op == 1 ? gate[i] / (1.0f + expf(-gate[i])) : 1.0f / (1.0f + expf(-gate[i]));
         out[i] = v;
     }
 }

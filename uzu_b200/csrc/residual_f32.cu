@@ -162,7 +162,8 @@ __global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route
 }
 
 // One CTA, a warp per row: `top` rounds, each picking the best (logit, lower index first) that comes after the previous pick in that
-// order, so no list of the picked experts is kept. Weights: exp(z - z_first) over the sum of the picked ones.
+// order, so no list of the picked experts is kept. Weights: exp(z - z_first) over the sum of the picked ones, or (weight_kind 1) the
+// sigmoid of every picked logit on its own. compact_weight gets the same weights in the expert-sorted order of the pair list.
 __global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_args a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_a
             if (!any) first = best_v;
             any = true;
             prev_v = best_v; prev_i = best_i;
-            const float w = expf(best_v - first);
+            const float w = a.weight_kind == 1 ? 1.0f / (1.0f + expf(-best_v)) : expf(best_v - first);
             sum += w;
             if (lane == 0) {
                 pe[r * a.top + s] = (uint16_t)best_i;
@@ -203,13 +204,19 @@ __global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_a
             }
         }
         __syncwarp();
-        if (lane < a.top) {
+        if (lane < a.top && a.weight_kind == 0) {
             for (uint32_t s = lane; s < a.top; s += 32) weight[r * a.top + s] /= sum;
         }
     }
     __syncthreads();
     route_sort_pairs(pe, counts, pairs, a.top, a.experts, reinterpret_cast<uint32_t*>(a.group_offsets), reinterpret_cast<uint32_t*>(a.rows_map),
                      reinterpret_cast<uint32_t*>(a.pair_pos));
+    if (a.compact_weight) {
+        __syncthreads();
+        const uint32_t* pos = reinterpret_cast<const uint32_t*>(a.pair_pos);
+        float* cw = reinterpret_cast<float*>(a.compact_weight);
+        for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) cw[pos[p]] = weight[p];
+    }
 }
 
 __global__ void routed_combine_kernel(const uzu_routed_combine_args a) {
