@@ -79,7 +79,8 @@ def window_softmax_attention(q, k, v, pos_q, pos_k, heads, kv_heads, scale, temp
     """q [Tq, heads, dim], k [Tk, kv_heads, dim], v [Tk, kv_heads, vdim] -> [Tq, heads, vdim]"""
     Tq, Tk = q.shape[0], k.shape[0]
     per = heads // kv_heads
-    mask = torch.tensor([[visible(int(i), int(j), size, keep_first) for j in pos_k] for i in pos_q])
+    pq, pk = torch.as_tensor(pos_q, dtype=torch.int64)[:, None], torch.as_tensor(pos_k, dtype=torch.int64)[None, :]
+    mask = (pk <= pq) & ((pq - pk < size) | (pk < keep_first))          # visible(i, j, ...) for all pairs at once
     out = torch.zeros(Tq, heads, v.shape[-1], dtype=F64)
     for h in range(heads):
         g = h // per
@@ -199,3 +200,70 @@ def forward(cfg, W, tokens, state=None, layer_outputs=None):
             layer_outputs.append(x.clone())
     state.pos += T
     return offset_norm(x, W["final.norm"], eps) @ W["head"].to(F64).T
+
+
+# ---- small configurations and random weights for the tests ----------------------------------------------------------------------------
+def moe_mlp(ff, experts, top):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def mingru_layer(width, mlp=None):
+    return {"type": "mingru", "mixer": {"width": width}, "mlp": mlp}
+
+
+def parallel_layer(heads, kv_heads, dim, vdim, size, keep_first, r_heads, r_dim, r_vdim, decay, mlp=None, rot_dims=None, base=10000.0, scale=None,
+                   softcap=15.0, left_scale=1.0, right_scale=1.0):
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5),
+            "softcap": float(softcap), "rot": {"base": float(base), "dims": dim if rot_dims is None else rot_dims},
+            "mask": {"size": size, "keep_first": keep_first}}
+    right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": [float(d) for d in decay]}
+    return {"type": "parallel", "mixer": {"left": left, "left_scale": float(left_scale), "right": right, "right_scale": float(right_scale)}, "mlp": mlp}
+
+
+def make_config(width, vocab, layers, eps=1e-6):
+    return {"architecture": "Vugipel", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": layers}
+
+
+def random_weights(cfg, seed=0):
+    """bf16 tensors (what a checkpoint holds), as a dict of torch tensors"""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def mat(rows, cols, gain=1.0):
+        return (torch.randn(rows, cols, generator=g) * gain / math.sqrt(cols)).to(torch.bfloat16)
+
+    def vec(n, mean=0.0, spread=0.1):
+        return (mean + spread * torch.randn(n, generator=g)).to(torch.bfloat16)
+
+    t = {"embed": mat(V, W, math.sqrt(W)), "head": mat(V, W, 2.0), "final.norm": vec(W)}
+    for i, lc in enumerate(cfg["layers"]):
+        p = "l%d." % i
+        mc = lc["mixer"]
+        t[p + "norm1"] = vec(W, 0.0, 0.2)
+        if lc["type"] == "mingru":
+            n = mc["width"]
+            t[p + "mix.z"], t[p + "mix.z.b"] = mat(n, W, 1.5), vec(n, 0.0, 0.7)
+            t[p + "mix.x"], t[p + "mix.x.b"] = mat(n, W, 1.5), vec(n, 0.0, 0.7)
+            t[p + "mix.g"], t[p + "mix.o"] = mat(n, W, 1.5), mat(W, n, 1.5)
+        else:
+            A, R = mc["left"], mc["right"]
+            H, G, D, Dv = A["heads"], A["kv_heads"], A["dim"], A["vdim"]
+            l, r = p + "mix.left.", p + "mix.right."
+            t[l + "q"], t[l + "q.b"] = mat(H * D, W), vec(H * D, 0.0, 0.3)
+            t[l + "k"], t[l + "k.b"] = mat(G * D, W), vec(G * D, 0.0, 0.3)
+            t[l + "v"], t[l + "v.b"] = mat(G * Dv, W), vec(G * Dv, 0.0, 0.3)
+            t[l + "q.norm"], t[l + "k.norm"] = vec(D, 1.0, 0.3), vec(D, 1.0, 0.3)
+            t[l + "temp"] = (0.3 + torch.rand(H, generator=g) * 1.5).to(torch.bfloat16)
+            t[l + "o"], t[l + "o.b"] = mat(W, H * Dv, 1.5), vec(W, 0.0, 0.2)
+            Hr, Dr, Dvr = R["heads"], R["dim"], R["vdim"]
+            t[r + "q"], t[r + "k"], t[r + "v"] = mat(Hr * Dr, W, 1.5), mat(Hr * Dr, W, 1.5), mat(Hr * Dvr, W)
+            t[r + "g"], t[r + "o"] = mat(Hr * Dvr, W, 1.5), mat(W, Hr * Dvr, 1.5)
+        ml = lc.get("mlp")
+        if ml:
+            t[p + "norm2"] = vec(W, 0.0, 0.2)
+            f, E = ml["expert"]["ff"], ml["router"]["experts"]
+            t[p + "mlp.router"] = mat(E, W, 3.0)
+            for x in range(E):
+                q = "%smlp.e%d." % (p, x)
+                t[q + "gate"], t[q + "up"], t[q + "down"] = mat(f, W, 1.5), mat(f, W, 1.5), mat(W, f, 1.5)
+    return t

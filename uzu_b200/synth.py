@@ -530,3 +530,99 @@ def gamanex_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=0, top=2,
         layers.append(gamanex_attention_layer(heads, kv, 128, 128, gamanex_dense_mlp(ff), q_temp=(0.2, 128)))
         layers.append(gamanex_attention_layer(heads, kv, 128, 128, mlp_b, q_temp=(0.2, 128), kv_from=2 * b))
     return gamanex_config(width, vocab, layers, eps=1e-5, logit_scale=0.5)
+
+
+# ---------------------------------------------------------------------------------------------
+# Vugipel (sequential pre-norm sublayers; minGRU, or window attention + retention side by side; sigmoid-routed experts weighted on their
+# input): config.json {"architecture": "Vugipel", "width", "vocab", "norm": {"eps"}, "layers": [{"type": "mingru" | "parallel", "mixer",
+# "mlp"}]}; tensors embed, head, final.norm, l<i>.norm1/2 (stored around zero), l<i>.mix.*, l<i>.mlp.*
+# ---------------------------------------------------------------------------------------------
+def vugipel_mingru_layer(width: int, mlp: dict | None) -> dict:
+    return {"type": "mingru", "mixer": {"width": width}, "mlp": mlp}
+
+
+def vugipel_parallel_layer(heads: int, kv_heads: int, dim: int, vdim: int, window: int, keep_first: int, r_heads: int, r_dim: int, r_vdim: int,
+                           mlp: dict | None, rot_dims: int | None = None, rot_base: float = 10000.0, scale: float | None = None,
+                           softcap: float = 30.0, decay: list | None = None, left_scale: float = 1.0, right_scale: float = 1.0) -> dict:
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5),
+            "softcap": float(softcap), "rot": {"base": float(rot_base), "dims": int(rot_dims if rot_dims is not None else dim)},
+            "mask": {"size": int(window), "keep_first": int(keep_first)}}
+    if decay is None:
+        decay = [1.0 - 2.0 ** -(5 + (h % 6)) for h in range(r_heads)]
+    right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": [float(d) for d in decay]}
+    return {"type": "parallel", "mixer": {"left": left, "left_scale": float(left_scale), "right": right, "right_scale": float(right_scale)}, "mlp": mlp}
+
+
+def vugipel_moe_mlp(ff: int, experts: int, top: int) -> dict:
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def vugipel_config(width: int, vocab: int, layers: list, eps: float = 1e-6) -> dict:
+    return {"architecture": "Vugipel", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": layers}
+
+
+def vugipel_tensors(config: dict, seed: int = 0) -> dict:
+    """Seeded random tensors of a Vugipel config: f32 values that bf16 holds exactly."""
+    rng = np.random.default_rng(seed)
+    W, V = config["width"], config["vocab"]
+
+    def bf(x):
+        return st_bits_to_f32(f32_to_bf16_bits(np.asarray(x, np.float32)))
+
+    def mat(rows, cols, gain=1.0):
+        return bf(rng.standard_normal((rows, cols), dtype=np.float32) * (gain / np.sqrt(cols)))
+
+    def vec(n, mean=0.0, spread=0.1):
+        return bf(mean + spread * rng.standard_normal(n, dtype=np.float32))
+
+    t = {"embed": mat(V, W, np.sqrt(W)), "head": mat(V, W, 2.0), "final.norm": vec(W)}
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        m = L["mixer"]
+        t[p + "norm1"] = vec(W)
+        if L["type"] == "mingru":
+            n = m["width"]
+            t[p + "mix.z"], t[p + "mix.z.b"] = mat(n, W, 1.5), vec(n, 0.0, 0.5)
+            t[p + "mix.x"], t[p + "mix.x.b"] = mat(n, W, 1.5), vec(n, 0.0, 0.5)
+            t[p + "mix.g"], t[p + "mix.o"] = mat(n, W, 1.5), mat(W, n)
+        else:
+            A, R = m["left"], m["right"]
+            H, G, D, Dv = A["heads"], A["kv_heads"], A["dim"], A["vdim"]
+            l, r = p + "mix.left.", p + "mix.right."
+            t[l + "q"], t[l + "q.b"] = mat(H * D, W), vec(H * D, 0.0, 0.2)
+            t[l + "k"], t[l + "k.b"] = mat(G * D, W), vec(G * D, 0.0, 0.2)
+            t[l + "v"], t[l + "v.b"] = mat(G * Dv, W), vec(G * Dv, 0.0, 0.2)
+            t[l + "q.norm"], t[l + "k.norm"] = vec(D, 1.0, 0.2), vec(D, 1.0, 0.2)
+            t[l + "temp"] = bf(np.abs(vec(H, 1.0, 0.3)) + 0.25)
+            t[l + "o"], t[l + "o.b"] = mat(W, H * Dv), vec(W, 0.0, 0.1)
+            Hr, Dr, Dvr = R["heads"], R["dim"], R["vdim"]
+            t[r + "q"], t[r + "k"], t[r + "v"] = mat(Hr * Dr, W), mat(Hr * Dr, W), mat(Hr * Dvr, W)
+            t[r + "g"], t[r + "o"] = mat(Hr * Dvr, W, 1.5), mat(W, Hr * Dvr)
+        ml = L.get("mlp")
+        if ml is None:
+            continue
+        t[p + "norm2"] = vec(W)
+        f, E = ml["expert"]["ff"], ml["router"]["experts"]
+        t[p + "mlp.router"] = mat(E, W, 2.0)
+        for x in range(E):
+            q = f"{p}mlp.e{x}."
+            t[q + "gate"], t[q + "up"], t[q + "down"] = mat(f, W, 1.5), mat(f, W, 1.5), mat(W, f)
+    return t
+
+
+def write_vugipel_model(config: dict, path, seed: int = 0, tensors: dict | None = None) -> Path:
+    """config.json + model.safetensors (bf16). `tensors` overrides the seeded random ones (values are rounded to bf16)."""
+    return write_punilix_model(config, path, seed, tensors if tensors is not None else vugipel_tensors(config, seed))
+
+
+def vugipel_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=8, top=2, window=1024, keep_first=4) -> dict:
+    """A layer stack of realistic sizes for benchmarks: per block one minGRU layer and one layer with window attention and retention side
+    by side, every layer with routed experts whose active size is `ff`."""
+    ff = ff or 4 * width
+    heads = max(width // 128, 1)
+    layers = []
+    for _ in range(blocks):
+        layers.append(vugipel_mingru_layer(width, vugipel_moe_mlp(ff // top, experts, top)))
+        layers.append(vugipel_parallel_layer(heads, max(heads // 4, 1), 128, 128, window, keep_first, max(heads // 2, 1), 128, 128,
+                                             vugipel_moe_mlp(ff // top, experts, top), softcap=30.0, left_scale=0.8, right_scale=1.1))
+    return vugipel_config(width, vocab, layers, eps=1e-5)
