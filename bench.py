@@ -715,7 +715,9 @@ FAMILY_SIZES = {
 def family_models(size: str, family: str = "punilix"):
     """[(name, checkpoint, stored bytes per weight)]: the family's model and the closest existing model's at one size: two layers per
     block of the same width, feed-forward size, head count and layer count; random weights. Punilix stands beside the 4-bit hybrid
-    (gated attention + DeltaNet); Gamanex (attention layers that keep or borrow their cache, dense feed-forwards) beside Punilix."""
+    (gated attention + DeltaNet); Gamanex (attention layers that keep or borrow their cache, dense feed-forwards) beside Punilix; Vugipel
+    (minGRU layers with one expert, window attention + retention layers with 2 of 8 routed experts) beside Punilix with a dense
+    feed-forward in its recurrent layers and 2 of 8 table-routed experts in its attention layers."""
     from uzu_b200 import synth
     width, ff, blocks, vocab = FAMILY_SIZES[size]
     base = Path(os.environ.get("UZU_MODEL_CACHE", "/dev/shm/uzu_b200_models"))
@@ -730,6 +732,15 @@ def family_models(size: str, family: str = "punilix"):
             synth.write_gamanex_model(synth.gamanex_preset(width=width, vocab=vocab, blocks=blocks, ff=ff), gdir, seed=0)
             (gdir / ".done").write_text("ok")
         return [("gamanex", gdir, 2.0), ("closest_existing", pdir, 2.0)]
+    if family == "vugipel":     # beside Punilix with routed experts of the same count and active size in the attention layers
+        vdir, mdir = base / f"vugipel-{size}", base / f"punilix-moe-{size}"
+        if not (vdir / ".done").exists():
+            synth.write_vugipel_model(synth.vugipel_preset(width=width, vocab=vocab, blocks=blocks, ff=ff, experts=8, top=2), vdir, seed=0)
+            (vdir / ".done").write_text("ok")
+        if not (mdir / ".done").exists():
+            synth.write_punilix_model(synth.punilix_preset(width=width, vocab=vocab, blocks=blocks, ff=ff, experts=8, top=2), mdir, seed=0)
+            (mdir / ".done").write_text("ok")
+        return [("vugipel", vdir, 2.0), ("closest_existing", mdir, 2.0)]
     heads = max(width // 128, 1)
     spec = synth.ModelSpec(name=f"hybrid-{size}", model_dim=width, hidden_dim=ff, vocab_size=vocab,
                            layer_kinds=["delta", "attn"] * blocks, num_heads=heads, num_groups=max(heads // 4, 1), head_dim=128,
@@ -759,7 +770,7 @@ def family_compare(args):
     with B.Context(0) as ctx:
         for size in sizes:
             models = family_models(size, args.family)
-            line = {"family_compare": size, "family": args.family, "closest_existing": "punilix (bf16)" if args.family == "gamanex" else "gated attention + DeltaNet hybrid (int4)", "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
+            line = {"family_compare": size, "family": args.family, "closest_existing": {"gamanex": "punilix (bf16)", "vugipel": "punilix with 2 of 8 table-routed experts (bf16)"}.get(args.family, "gated attention + DeltaNet hybrid (int4)"), "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
                                                                                                          "tensor_tflops": tens, "tensor_source": tens_src}}
             for name, d, bytes_per_weight in models:
                 with B.Engine(ctx, d, max_context_length=prompt_len + steps + 64, use_cuda_graph=not args.no_graph) as eng:
@@ -807,7 +818,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="decode this many independent sequences together (<= 16), one weight pass per step")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size: shard ONE model over this many ranks (= --gpus) instead of replicas")
-    ap.add_argument("--family", choices=["punilix", "gamanex"], default=None,
+    ap.add_argument("--family", choices=["punilix", "gamanex", "vugipel"], default=None,
                     help="instead of the headline workload: prefill / decode throughput of this model family beside the closest existing one at equal layer sizes (1 GPU)")
     ap.add_argument("--family-sizes", default="", help="comma list of " + ", ".join(sorted(FAMILY_SIZES)) + " (default 1k,2k)")
     args = ap.parse_args()

@@ -228,11 +228,14 @@ def new_cache(ctx, positions, kv_heads, dim, vdim, f32_cache):
 
 @pytest.mark.parametrize("T,prefix,heads,kv_heads,dim,vdim,rot_dims,window,keep", [
     (40, 0, 4, 2, 16, 24, 16, 7, 2), (9, 31, 6, 3, 48, 96, 48, 20, 4), (70, 5, 2, 2, 10, 6, 4, 16, 0), (33, 0, 3, 1, 64, 32, 32, 1, 3),
-    (130, 20, 2, 1, 128, 128, 64, 50, 1), (20, 0, 1, 1, 9, 14, 8, 0, 0), (25, 40, 2, 2, 24, 8, 24, 100, 5), (12, 3, 2, 1, 300, 40, 300, 6, 6)])
+    (130, 20, 2, 1, 128, 128, 64, 50, 1), (20, 0, 1, 1, 9, 14, 8, 0, 0), (25, 40, 2, 2, 24, 8, 24, 100, 5), (12, 3, 2, 1, 300, 40, 300, 6, 6),
+    (200, 0, 4, 2, 64, 32, 64, 70, 3), (150, 37, 2, 1, 48, 96, 48, 20, 4), (300, 100, 2, 2, 16, 16, 8, 0, 0), (260, 0, 1, 1, 32, 64, 32, 1, 70),
+    (70, 700, 2, 1, 64, 64, 64, 128, 5), (64, 1, 2, 2, 16, 112, 16, 63, 65)])
 @pytest.mark.parametrize("f32_cache", [True, False])
 def test_window_attention_kernels(ctx, T, prefix, heads, kv_heads, dim, vdim, rot_dims, window, keep, f32_cache):
     """Prompt rows on an empty cache and rows after a prefix, windows shorter and longer than the context, windows of one key, no window,
-    more kept tokens than the window is long, partial rotation, odd head sizes, grouped heads; with key splits of 0 / 2 / 5 / 64."""
+    more kept tokens than the window is long, partial rotation, odd head sizes, grouped heads; with key splits of 0 / 2 / 5 / 64. bf16 caches
+    with passes of >= 64 rows and head sizes in multiples of 16 take the tensor-pipe kernel (no splits), the rest the plain one."""
     rng = np.random.default_rng(T + dim)
     n = prefix + T
     q, k, v = (rng.standard_normal((n, w)).astype(np.float32) * 2 for w in (heads * dim, kv_heads * dim, kv_heads * vdim))
@@ -265,7 +268,7 @@ def test_one_key_at_the_edges_of_the_window_and_of_the_kept_tokens(ctx, f32_cach
     """Among 700 keys one is made to stand out (its score is far above the others: key and query share one large channel, no rotation on
     it). Queried from position p, the output is that key's value when it is visible and something else when it is not: the key sits just
     inside / just outside the window, is the last kept token / the first one not kept, or is position 0 far outside the window."""
-    heads, dim, vdim, window, keep = 2, 16, 8, 64, 3
+    heads, dim, vdim, window, keep = 2, 16, 16, 64, 3         # bf16 prompt rows take the tensor-pipe kernel, everything else the plain one
     rng = np.random.default_rng(11)
     n = 700
     for place, p, seen in [(n - window, n - 1, True), (n - window - 1, n - 1, False), (keep - 1, n - 1, True), (keep, n - 1, False), (0, 500, True),
@@ -299,7 +302,7 @@ def config_a():
     a layer without feed-forward; layer order gru, parallel, parallel, gru."""
     return P.make_config(96, 211, [
         P.mingru_layer(56, P.moe_mlp(20, 6, 2)),
-        P.parallel_layer(6, 2, 16, 24, 11, 2, 3, 20, 12, [0.9, 0.96875, 1.0], mlp=P.moe_mlp(28, 4, 1), rot_dims=8, base=300.0, scale=0.21, softcap=8.0,
+        P.parallel_layer(6, 2, 16, 32, 11, 2, 3, 20, 12, [0.9, 0.96875, 1.0], mlp=P.moe_mlp(28, 4, 1), rot_dims=8, base=300.0, scale=0.21, softcap=8.0,
                          left_scale=0.7, right_scale=1.2),
         P.parallel_layer(2, 2, 24, 10, 40, 0, 2, 12, 28, [0.5, 0.99], mlp=None, softcap=25.0, left_scale=1.3, right_scale=0.6),
         P.mingru_layer(72, P.moe_mlp(12, 3, 3)),
@@ -392,7 +395,7 @@ def test_decode_and_portions_match_the_whole_prompt(ctx, tmp_path, make, f32):
     """Prefill + token-by-token decoding (the window passes over decoded tokens), and portions of 2, 3, 1, 33, 2, ... tokens cut in the middle
     of windows, give the logits of the whole prompt."""
     pr = Pair(ctx, tmp_path, make(), seed=2, f32=f32)
-    n = 90
+    n = 170
     toks = tokens_for(pr.config, n, 2)
     ref = pr.reference(toks)
     s = pr.engine.slot_acquire()
@@ -402,7 +405,7 @@ def test_decode_and_portions_match_the_whole_prompt(ctx, tmp_path, make, f32):
     pr.engine.slot_release(s)
     s = pr.engine.slot_acquire()                 # the same slot again: its cache rows and states start over
     parts, p, k = [], 0, 0
-    sizes = [2, 3, 1, 33, 2, 9, 32, 2]
+    sizes = [2, 3, 1, 33, 2, 70, 9, 32, 2]       # 70 rows after a prefix of 41: the tensor-pipe attention with rows before it in the cache
     while p < n:
         c = min(sizes[k % len(sizes)], n - p)
         parts.append(pr.engine.forward_rows(toks[p:p + c], list(range(c)), slot=s))

@@ -44,6 +44,7 @@ SOURCES = {
     "latent_attention.cu": [],
     "sigmoid_attention.cu": [],
     "window_attention.cu": [],
+    "window_attention_mma.cu": [],
     "linear_recurrence.cu": [],
     "engine.cu": [],
 }

@@ -189,8 +189,11 @@ void uzu_retention_encode(uzu_command_buffer* cmd, const uzu_retention_args* a) 
     const uint32_t parts = (b.dim + part - 1) / part;
     const size_t smem = ((size_t)2 * RT_BATCH * b.dim + (size_t)RT_BATCH * 32 + (size_t)RT_BATCH * parts * 32) * sizeof(float);
     const dim3 grid((b.vdim + 31) / 32, b.heads), block(parts * 32);
+    // the opt-in is made once per instance and device: for the longest keys the instance serves (32 warps of `part` channels)
+    const uint32_t dim_most = std::min(1024u, (uint32_t)part * 32u);
+    const size_t smem_most = ((size_t)2 * RT_BATCH * dim_most + (size_t)RT_BATCH * 32 + (size_t)RT_BATCH * 32 * 32) * sizeof(float);
     auto go = [&](auto kernel, std::atomic<uint64_t>& done) {
-        if (smem > 48 * 1024) opt_in_dynamic_smem(cmd, kernel, (int)smem, done);
+        opt_in_dynamic_smem(cmd, kernel, (int)smem_most, done);
         launch(cmd, "retention_kernel", kernel, grid, block, smem, b);
     };
     static std::atomic<uint64_t> done[4];

@@ -128,16 +128,31 @@ __device__ void route_sort_pairs(const uint16_t* pe, uint32_t* counts, uint32_t 
     }
     __syncthreads();
     for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = counts[e];
-    // stable placement: thread e walks the pairs in order and places those of expert e
-    for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
-        uint32_t at = counts[e];
-        if (counts[e + 1] == at) continue;
-        for (uint32_t p = 0; p < pairs; ++p) {
-            if (pe[p] == e) {
-                rows_map[at] = p / top;
-                pair_pos[p] = at;
-                ++at;
+    __syncthreads();
+    // Stable placement, counts[e] now being the next free position of expert e: pairs are taken in chunks of one per thread, the warps of
+    // a chunk one after the other; within a warp the lanes that hold the same expert are ranked by lane and their leader moves the cursor.
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (uint32_t base = 0; base < pairs; base += blockDim.x) {
+        const uint32_t p = base + threadIdx.x;
+        const bool valid = p < pairs;
+        const uint32_t e = valid ? pe[p] : 0x10000u + lane;          // idle lanes match nobody
+        const uint32_t busy = min(warps, (pairs - base + 31) / 32);
+        for (uint32_t w = 0; w < busy; ++w) {
+            if (warp == w) {
+                const uint32_t same = __match_any_sync(0xffffffffu, e);
+                const uint32_t rank = __popc(same & ((1u << lane) - 1u));
+                uint32_t at = 0;
+                if (valid && rank == 0) {
+                    at = counts[e];
+                    counts[e] = at + __popc(same);
+                }
+                at = __shfl_sync(0xffffffffu, at, __ffs(same) - 1);
+                if (valid) {
+                    rows_map[at + rank] = p / top;
+                    pair_pos[p] = at + rank;
+                }
             }
+            __syncthreads();
         }
     }
 }

@@ -541,8 +541,10 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const uzu_si
 template <int DK, int DV>
 static void launch_sigmoid_attention_mma(uzu_command_buffer* cmd, const uzu_sigmoid_attention_args& a) {
     const size_t smem = ((size_t)4 * SM_BM * (a.dim + SM_PAD) + (size_t)2 * SM_BN * (a.vdim + SM_PAD)) * sizeof(__nv_bfloat16);
+    // the opt-in is made once per instance and device: for the largest head sizes the instance serves
+    constexpr size_t smem_most = ((size_t)4 * SM_BM * (DK * 16 + SM_PAD) + (size_t)2 * SM_BN * (DV * 16 + SM_PAD)) * sizeof(__nv_bfloat16);
     static std::atomic<uint64_t> opt_in{0};
-    opt_in_dynamic_smem(cmd, sigmoid_attention_mma_kernel<DK, DV>, (int)smem, opt_in);
+    opt_in_dynamic_smem(cmd, sigmoid_attention_mma_kernel<DK, DV>, (int)smem_most, opt_in);
     uint32_t ctas = 0;                           // (row tile, chunk) pairs
     for (uint32_t mt = 0; mt < (a.rows + SM_BM - 1) / SM_BM; ++mt) {
         const uint32_t nt = (a.prefix + std::min(a.rows, (mt + 1) * SM_BM) + SM_BN - 1) / SM_BN;

@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(128) window_attention_prepare_kernel(const uzu
     }
 }
 
-constexpr int WA_WARPS = 4, WA_TILE = 16, WA_UNROLL = 4;
+constexpr int WA_WARPS = 4, WA_TILE = 16, WA_UNROLL = 4, WA_MAX_SPLITS = 128;
 
 // WPL = words of a head's key / value row per lane (the larger of the two)
 template <typename T, int EPW, int WPL>
@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attention_kernel(const u
     extern __shared__ float wa_smem[];          // [WA_WARPS][vdim] partial sums, then [vdim] the head's result
     __shared__ float warp_m[WA_WARPS], warp_l[WA_WARPS];
     __shared__ uint32_t is_last;
+    __shared__ float split_f[WA_MAX_SPLITS], split_l[WA_MAX_SPLITS];
     const uint32_t t = blockIdx.x, h = blockIdx.y, split = blockIdx.z, splits = gridDim.z;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
@@ -258,19 +259,29 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attention_kernel(const u
         if (!is_last) return;
         __threadfence();
         const float* parts = reinterpret_cast<const float*>(a.partials) + ((size_t)t * a.heads + h) * splits * pw;
-        float all_m = -INFINITY;
-        for (uint32_t sp = 0; sp < splits; ++sp) all_m = fmaxf(all_m, __ldcg(parts + (size_t)sp * pw));
-        float all_l = 0.0f;
-        for (uint32_t sp = 0; sp < splits; ++sp) {
-            const float m = __ldcg(parts + (size_t)sp * pw);
-            if (m != -INFINITY) all_l = fmaf(__ldcg(parts + (size_t)sp * pw + 1), expf(m - all_m), all_l);
+        for (uint32_t sp = tid; sp < splits; sp += blockDim.x) {
+            split_f[sp] = __ldcg(parts + (size_t)sp * pw);
+            split_l[sp] = __ldcg(parts + (size_t)sp * pw + 1);
         }
+        __syncthreads();
+        float all_m = -INFINITY;
+        for (uint32_t sp = 0; sp < splits; ++sp) all_m = fmaxf(all_m, split_f[sp]);
+        __syncthreads();
+        for (uint32_t sp = tid; sp < splits; sp += blockDim.x) split_f[sp] = split_f[sp] == -INFINITY ? 0.0f : expf(split_f[sp] - all_m);
+        __syncthreads();
+        float all_l = 0.0f;
+        for (uint32_t sp = 0; sp < splits; ++sp) all_l = fmaf(split_l[sp], split_f[sp], all_l);      // in split order
         for (uint32_t c = tid; c < a.vdim; c += blockDim.x) {
             float v = 0.0f;
-            for (uint32_t sp = 0; sp < splits; ++sp) {       // in split order
-                const float m = __ldcg(parts + (size_t)sp * pw);
-                if (m != -INFINITY) v = fmaf(__ldcg(parts + (size_t)sp * pw + 2 + c), expf(m - all_m), v);
+            uint32_t sp = 0;
+            for (; sp + 8 <= splits; sp += 8) {        // eight loads in flight, added in split order
+                float x[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) x[u] = __ldcg(parts + (size_t)(sp + u) * pw + 2 + c);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v = fmaf(x[u], split_f[sp + u], v);
             }
+            for (; sp < splits; ++sp) v = fmaf(__ldcg(parts + (size_t)sp * pw + 2 + c), split_f[sp], v);
             result[c] = v / all_l;
         }
         if (tid == 0) *ticket = 0;
@@ -293,6 +304,8 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attention_kernel(const u
         }
     }
 }
+
+bool encode_window_attention_mma(uzu_command_buffer* cmd, const uzu_window_attention_args& a);     // window_attention_mma.cu
 
 }  // namespace uzu
 
@@ -328,11 +341,12 @@ void uzu_window_attention_encode(uzu_command_buffer* cmd, const uzu_window_atten
         return;
     }
     if (a->rows == 0) return;
-    uint32_t splits = a->splits ? a->splits : 1;
+    uint32_t splits = std::min<uint32_t>(a->splits ? a->splits : 1, WA_MAX_SPLITS);
     if (splits > 1 && (!a->partials || !a->tickets)) {
         cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "window_attention: key splits need the partials and tickets scratch");
         return;
     }
+    if (splits == 1 && encode_window_attention_mma(cmd, *a)) return;
     const bool f32 = a->cache_dt == UZU_DT_F32;
     // bf16 rows of even head sizes are read two elements per word
     const bool pairs = !f32 && a->dim % 2 == 0 && a->vdim % 2 == 0;

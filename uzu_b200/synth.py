@@ -616,13 +616,14 @@ def write_vugipel_model(config: dict, path, seed: int = 0, tensors: dict | None 
 
 
 def vugipel_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=8, top=2, window=1024, keep_first=4) -> dict:
-    """A layer stack of realistic sizes for benchmarks: per block one minGRU layer and one layer with window attention and retention side
-    by side, every layer with routed experts whose active size is `ff`."""
+    """A layer stack of realistic sizes for benchmarks: per block one minGRU layer whose feed-forward is a single expert of size `ff` (the
+    design's dense feed-forward) and one layer with window attention and retention side by side with `top` of `experts` routed experts of
+    the same active size."""
     ff = ff or 4 * width
     heads = max(width // 128, 1)
     layers = []
     for _ in range(blocks):
-        layers.append(vugipel_mingru_layer(width, vugipel_moe_mlp(ff // top, experts, top)))
+        layers.append(vugipel_mingru_layer(width, vugipel_moe_mlp(ff, 1, 1)))
         layers.append(vugipel_parallel_layer(heads, max(heads // 4, 1), 128, 128, window, keep_first, max(heads // 2, 1), 128, 128,
                                              vugipel_moe_mlp(ff // top, experts, top), softcap=30.0, left_scale=0.8, right_scale=1.1))
     return vugipel_config(width, vocab, layers, eps=1e-5)
