@@ -169,6 +169,28 @@ def test_sigmoid_router_weights_scale_the_expert_input(ctx, rows, experts, top, 
             close(got[pos[r, s]], ref.numpy(), 2e-5 if f32_weights or rows < 32 else 2e-2, f"pair ({r}, {s})")
 
 
+@pytest.mark.parametrize("m", [3, 40, 130, 300])
+@pytest.mark.parametrize("f32_weights", [True, False])
+def test_product_with_bias_row_scale_and_share(ctx, m, f32_weights):
+    """D += share * row_scale[r] * (A . W^T) + bias: the stacked projections' biases and an output projection's share of a sum, in the short-pass,
+    tile, tensor-pipe and tensor-memory forms (the last from 128 rows on with bf16 weights)."""
+    rng = np.random.default_rng(m)
+    n, k = 192, 128
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = bf16_exact(rng.standard_normal((n, k)) / 8)
+    bias, rs = rng.standard_normal(n).astype(np.float32), (0.2 + rng.random(m)).astype(np.float32)
+    d0 = rng.standard_normal((m, n)).astype(np.float32)
+    bx, bw = ctx.upload(x), ctx.upload(w if f32_weights else synth.f32_to_bf16_bits(w))
+    bb, br, bd, ws = ctx.upload(bias), ctx.upload(rs), ctx.upload(d0), ctx.upload(np.zeros((m, k), np.uint16))
+    a = B.DenseLinearArgs(a=bx.ptr, w=bw.ptr, d=bd.ptr, bias=bb.ptr, row_scale=br.ptr, workspace=ws.ptr, m=m, n=n, k=k, lda=k, ldd=n, batch=1,
+                          weights_dt=B.DT_F32 if f32_weights else B.DT_BF16, accumulate=1, scale=0.8)
+    run(ctx, "uzu_dense_linear_encode", C.byref(a))
+    act = t64(x) if f32_weights or m < 32 else t64(bf16_exact(x))
+    ref = t64(d0) + 0.8 * t64(rs)[:, None] * (act @ t64(w).T) + t64(bias)
+    close(bd.numpy(np.float32, d0.shape), ref.numpy(), 5e-6, "bias, row scale, share")
+    assert ctx.lib.uzu_debug_dense_umma_error() == 0
+
+
 def rope_table(positions, pairs, base, dims):
     ang = np.arange(positions, dtype=np.float64)[:, None] * base ** (-2.0 * np.arange(pairs, dtype=np.float64) / dims)
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)

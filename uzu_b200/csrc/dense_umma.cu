@@ -23,6 +23,8 @@ struct DenseUmmaParams {
     const float* gate;         // optional [m, gate_ld]
     const float* gate_bias;    // optional [n], added to the gate
     const float* col_scale;    // optional [n]
+    const float* bias;         // optional [n], added after scale / gate / col_scale
+    const float* row_scale;    // optional [m]
     uint32_t m, n, k, ldd, gate_ld, accumulate;
     float scale;
     uint32_t desc_hi, desc_lbo, k_step, idesc;
@@ -167,12 +169,15 @@ __global__ void __launch_bounds__(DU_NP + 32, 1) dense_umma_kernel(const DenseUm
                 if (row >= p.m || col0 >= p.n) continue;
                 float* out = p.d + (size_t)row * p.ldd + col0;
                 const float* gate = p.gate ? p.gate + (size_t)row * p.gate_ld + col0 : nullptr;
+                const float rs = p.row_scale ? p.row_scale[row] : 1.0f;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     if (col0 + (uint32_t)j < p.n) {
                         float val = __uint_as_float(v[j]) * p.scale;
+                        if (p.row_scale) val *= rs;
                         if (gate) val *= 1.0f / (1.0f + expf(-(gate[j] + (p.gate_bias ? p.gate_bias[col0 + j] : 0.0f))));
                         if (p.col_scale) val *= p.col_scale[col0 + j];
+                        if (p.bias) val += p.bias[col0 + j];
                         if (p.accumulate) val += out[j];
                         out[j] = val;
                     }
@@ -233,11 +238,11 @@ __global__ void dense_cast_bf16_kernel(const float* a, uint32_t lda, __nv_bfloat
     *reinterpret_cast<uint2*>(out + idx) = o;
 }
 
-// Shapes the tensor-memory kernel takes: one plain product (no z-batches, row groups or bias), bf16 weights, >= 128 rows, k a multiple
+// Shapes the tensor-memory kernel takes: one plain product (no z-batches or row groups), bf16 weights, >= 128 rows, k a multiple
 // of 64, 16-byte aligned operands, and a bf16 workspace of m * k elements from the caller.
 bool dense_umma_applicable(const uzu_dense_linear_args& a) {
     static const bool off = getenv("UZU_DENSE_NO_UMMA") != nullptr;      // A/B runs
-    if (off || !a.workspace || a.weights_dt != UZU_DT_BF16 || a.batch != 1 || a.group_offsets || a.rows_map || a.bias || a.pair_rows || a.row_scale) return false;
+    if (off || !a.workspace || a.weights_dt != UZU_DT_BF16 || a.batch != 1 || a.group_offsets || a.rows_map || a.pair_rows) return false;
     if (a.m < 128 || a.k % 64u != 0 || a.n < 64) return false;
     if ((a.a & 15u) || (a.w & 15u) || (a.workspace & 15u) || a.lda % 4u != 0) return false;
     return true;
@@ -254,6 +259,8 @@ void encode_dense_umma(uzu_command_buffer* cmd, const uzu_dense_linear_args& a) 
     p.gate = (const float*)a.gate;
     p.gate_bias = (const float*)a.gate_bias;
     p.col_scale = (const float*)a.col_scale;
+    p.bias = (const float*)a.bias;
+    p.row_scale = (const float*)a.row_scale;
     p.m = a.m; p.n = a.n; p.k = a.k; p.ldd = a.ldd; p.gate_ld = a.gate_ld; p.accumulate = a.accumulate;
     p.scale = a.scale;
     // shared-memory matrix descriptor: start address >> 4 @ [0,14), LBO >> 4 @ [16,30), SBO >> 4 @ [32,46), version 1 @ [46,48), layout

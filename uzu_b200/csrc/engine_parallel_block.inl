@@ -989,15 +989,25 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
         ra.pair_pos = P.pair_pos.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts; ra.vocab = e->vocab;
         uzu_table_route_encode(cmd, &ra);
     }
+    // a single expert takes every row in row order: its two products are plain ones (no row groups), so long passes run them on tcgen05
+    const bool grouped = M.experts > 1;
     uzu_dense_linear_args up = gate_up_args();
-    up.batch = M.experts; up.w_z_stride = M.gate_up.stride();
-    up.group_offsets = P.group_offsets.ptr(); up.rows_map = P.rows_map.ptr();
+    if (grouped) {
+        up.batch = M.experts; up.w_z_stride = M.gate_up.stride();
+        up.group_offsets = P.group_offsets.ptr(); up.rows_map = P.rows_map.ptr();
+    }
     uzu_dense_linear_encode(cmd, &up);
     if (!paired) unit(m * M.top);
-    uzu_dense_linear_args dn = dense_args(e, M.down, P.act.ptr(), m, P.pair_out.ptr());
-    dn.lda = M.f; dn.batch = M.experts; dn.w_z_stride = M.down.stride();
-    dn.group_offsets = P.group_offsets.ptr();
+    // ... and, when its weight already sits on its input and no sublayer gate follows, its down projection adds straight into the residual
+    const bool direct = !grouped && M.weight_on_input && !L.mlp_gate.present;
+    uzu_dense_linear_args dn = dense_args(e, M.down, P.act.ptr(), m, direct ? P.resid.ptr() : P.pair_out.ptr());
+    dn.lda = M.f; dn.accumulate = direct ? 1 : 0;
+    if (grouped) {
+        dn.batch = M.experts; dn.w_z_stride = M.down.stride();
+        dn.group_offsets = P.group_offsets.ptr();
+    }
     uzu_dense_linear_encode(cmd, &dn);
+    if (direct) return;
     uzu_routed_combine_args ca{};
     ca.pairs = P.pair_out.ptr(); ca.pair_pos = P.pair_pos.ptr(); ca.output = P.resid.ptr(); ca.rows = m; ca.top = M.top; ca.n = W; ca.accumulate = 1;
     if (M.kind == GatedMlp::RoutedExperts) { ca.pair_weight = M.weight_on_input ? 0 : P.pair_weight.ptr(); ca.weight = 1.0f; }
