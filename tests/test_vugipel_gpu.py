@@ -343,10 +343,10 @@ def config_b():
 
 def config_c():
     """Sizes that fit no vector width: width 90, head sizes 10 / 6 and 18 / 22 (bf16 rows that start at odd words), odd feed-forwards, 3 experts,
-    retention keys of 9 with values of 7, a gru of 35."""
+    retention keys of 9 with values of 7, a gru of 35 followed by a single expert (plain products that add straight into the residual)."""
     return P.make_config(90, 77, [
         P.parallel_layer(4, 2, 10, 6, 9, 3, 3, 9, 7, [0.9, 0.95, 0.99], mlp=P.moe_mlp(11, 3, 2), rot_dims=6, base=50.0, scale=0.4, softcap=12.0),
-        P.mingru_layer(35, P.moe_mlp(51, 2, 1)),
+        P.mingru_layer(35, P.moe_mlp(51, 1, 1)),
         P.parallel_layer(2, 1, 18, 22, 30, 1, 1, 33, 5, [0.97], mlp=None, left_scale=0.5, right_scale=2.0),
     ], eps=1e-5)
 
