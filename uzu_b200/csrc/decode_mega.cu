@@ -6,7 +6,7 @@
 // stream from empty). Here the weight stream never stops:
 //   * one CTA per SM, MK_NCW consumer warps + 1 producer warp. The producer warp walks the CTA's static schedule of weight units
 //     (16 rows x 512 nibbles = 4608 B incl. per-group coefficients) and feeds per-warp shared-memory rings with cp.async.bulk (TMA bulk
-//     copies, UBLKCP in SASS) completing on mbarriers. It does NOT take part in the grid barriers: weights never depend on
+//     copies) completing on mbarriers. It does NOT take part in the grid barriers: weights never depend on
 //     activations, so while the consumers wait at a barrier / stage the next activation row the rings already hold the next
 //     phase's first units (the whole ring of all SMs is ~22 MB: for Qwen3.5-0.8B that is more than a full layer).
 //   * weights are read from a decode-stream copy built once at load (mega_repack_kernel): unit-major, each unit exactly in the order

@@ -817,7 +817,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
 // METHOD / BITS / FUSED are compile-time so that the hot loop carries one dequantisation variant and the plain GEMV carries no
-// prologue / epilogue code: the first single-instance version was ~10.5 K SASS instructions and stalled mostly on instruction
+// prologue / epilogue code: the first single-instance version was very large and stalled mostly on instruction
 // fetch (ncu: no_instruction was the top stall at 1-2 warps per scheduler).
 // PRO: 0 none, 1 RMSNorm (+ residual add), 3 sigmoid gate (prologue 2, gated act, moved to the producer's epilogue); EPI: GatedActMul
 template <int NPG, int STAGES, int METHOD, int BITS, int PRO, bool EPI>
