@@ -8,6 +8,7 @@ magnitude above them) and in the serving precisions (bf16 products and caches).
 import ctypes as C
 import json
 import math
+from pathlib import Path
 
 import numpy as np
 import pytest
@@ -20,6 +21,7 @@ from uzu_b200 import synth
 
 pytestmark = pytest.mark.gpu
 F64 = torch.float64
+ROOT = Path(__file__).resolve().parents[1]
 
 
 def t64(a):
@@ -599,7 +601,6 @@ def test_trace_runner_command_line(tmp_path, dtype):
     logits of the wanted places in <step>.f32; the second request reuses the first one's slot."""
     import subprocess
     import sys
-    from pathlib import Path
     cfg = config_a()
     w = P.random_weights(cfg, 9)
     model = write_model(tmp_path / "model", cfg, w)
@@ -616,7 +617,7 @@ def test_trace_runner_command_line(tmp_path, dtype):
             wanted.append((step, rid, [at + x for x in want]))
             at, k, step = at + c, k + 1, step + 1
     out = tmp_path / "out"
-    root = Path(__file__).resolve().parents[1]
+    root = ROOT
     r = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
                        input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stderr[-2000:]
