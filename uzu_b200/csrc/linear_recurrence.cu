@@ -8,8 +8,9 @@
 // Retention (per head, state S [dim, vdim]):   S_t = decay S_(t-1) + (key_scale k_t) v_t^T,  out_t = S_t^T q_t
 //   The state update of an element needs no other thread: only the output is a sum over key channels, and it does not feed back. Grid
 //   (blocks of 32 value columns, heads); warp p owns PART key channels, lane c one value column, the slice of the state stays in
-//   registers. Tokens are taken in batches of RT_BATCH: q and k rows of the batch go to shared memory, every thread runs the batch with
-//   no barrier, leaving per-warp partial outputs in shared memory, which are then added in warp order (a fixed order).
+//   registers. Tokens are taken in batches of RT_BATCH: q and k rows of the batch go to shared memory (requested one batch ahead), every
+//   thread runs the batch with no barrier, leaving per-warp partial outputs in shared memory, which are then added in warp order (a
+//   fixed order).
 #include "common.cuh"
 
 namespace uzu {
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(32 * GRU_CHUNKS) min_gru_kernel(const uzu_min_
 constexpr int RT_BATCH = 16;
 
 template <int PART>
-__global__ void __launch_bounds__(1024) retention_kernel(const uzu_retention_args a) {
+__global__ void __launch_bounds__(PART == 32 ? 1024 : 512) retention_kernel(const uzu_retention_args a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float rt_smem[];
@@ -106,32 +107,79 @@ __global__ void __launch_bounds__(1024) retention_kernel(const uzu_retention_arg
     const float* pk = reinterpret_cast<const float*>(a.k) + (size_t)head * dim;
     const float* pv = reinterpret_cast<const float*>(a.v) + (size_t)head * vdim;
     float* out = reinterpret_cast<float*>(a.out) + (size_t)head * vdim;
+    // A batch's rows are requested one batch ahead into registers (dim <= 32 warps x PART, so a thread stages at most PART / 2 elements
+    // of q and of k and one of v), stored to shared memory at the top of the batch: the loads fly during the previous batch's walk.
+    constexpr int STAGE = PART / 2 > 1 ? PART / 2 : 1;
+    float pre_q[STAGE], pre_k[STAGE], pre_v[4];       // a CTA has at least 4 warps: 4 x 128 covers the batch's 16 x 32 values
+    auto request = [&](uint32_t tb) {
+        const uint32_t nb = tb < a.rows ? min((uint32_t)RT_BATCH, a.rows - tb) : 0u;
+#pragma unroll
+        for (int u = 0; u < STAGE; ++u) {
+            const uint32_t i = tid + (uint32_t)u * blockDim.x;
+            pre_q[u] = pre_k[u] = 0.0f;
+            if (i < nb * dim) {
+                const uint32_t r = i / dim, ch = i - r * dim;
+                pre_q[u] = pq[(size_t)(tb + r) * a.q_stride + ch];
+                pre_k[u] = pk[(size_t)(tb + r) * a.k_stride + ch] * a.key_scale;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t i = tid + (uint32_t)u * blockDim.x, r = i >> 5, cc = blockIdx.x * 32 + (i & 31);
+            pre_v[u] = (i < nb * 32 && cc < vdim) ? pv[(size_t)(tb + r) * a.v_stride + cc] : 0.0f;
+        }
+    };
+    const bool vec = (dim % 4 == 0) && (PART % 4 == 0);
+    request(0);
     for (uint32_t tb = 0; tb < a.rows; tb += RT_BATCH) {
         const uint32_t nb = min((uint32_t)RT_BATCH, a.rows - tb);
-        for (uint32_t i = tid; i < nb * dim; i += blockDim.x) {
-            const uint32_t r = i / dim, ch = i - r * dim;
-            qs[i] = pq[(size_t)(tb + r) * a.q_stride + ch];
-            ks[i] = pk[(size_t)(tb + r) * a.k_stride + ch] * a.key_scale;
+#pragma unroll
+        for (int u = 0; u < STAGE; ++u) {
+            const uint32_t i = tid + (uint32_t)u * blockDim.x;
+            if (i < RT_BATCH * dim) { qs[i] = pre_q[u]; ks[i] = pre_k[u]; }
         }
-        for (uint32_t i = tid; i < nb * 32; i += blockDim.x) {
-            const uint32_t r = i >> 5, cc = blockIdx.x * 32 + (i & 31);
-            vs[i] = cc < vdim ? pv[(size_t)(tb + r) * a.v_stride + cc] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const uint32_t i = tid + (uint32_t)u * blockDim.x;
+            if (i < RT_BATCH * 32) vs[i] = pre_v[u];
         }
         __syncthreads();
-        for (uint32_t r = 0; r < nb; ++r) {
-            const float vv = vs[r * 32 + lane];
-            const float* kr = ks + r * dim + i0;
-            const float* qr = qs + r * dim + i0;
-            float op = 0.0f;
+        request(tb + RT_BATCH);
+        const float* kr = ks + i0;
+        const float* qr = qs + i0;
+        float* mine = part + warp * 32 + lane;
+        if (vec && cnt == PART) {       // the common case: all of the warp's channels exist, 16-byte reads, no predicates
+            for (uint32_t r = 0; r < nb; ++r, kr += dim, qr += dim, mine += parts * 32) {
+                const float vv = vs[r * 32 + lane];
+                float op = 0.0f;
 #pragma unroll
-            for (int i = 0; i < PART; ++i) {
-                if ((uint32_t)i < cnt) {
-                    const float s = fmaf(kr[i], vv, decay * S[i]);
-                    S[i] = s;
-                    op = fmaf(s, qr[i], op);
+                for (int i = 0; i < PART; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kr + i), q4 = *reinterpret_cast<const float4*>(qr + i);
+                    S[i] = fmaf(k4.x, vv, decay * S[i]);
+                    S[i + 1] = fmaf(k4.y, vv, decay * S[i + 1]);
+                    S[i + 2] = fmaf(k4.z, vv, decay * S[i + 2]);
+                    S[i + 3] = fmaf(k4.w, vv, decay * S[i + 3]);
+                    op = fmaf(S[i], q4.x, op);
+                    op = fmaf(S[i + 1], q4.y, op);
+                    op = fmaf(S[i + 2], q4.z, op);
+                    op = fmaf(S[i + 3], q4.w, op);
                 }
+                *mine = op;
             }
-            part[(r * parts + warp) * 32 + lane] = op;
+        } else {
+            for (uint32_t r = 0; r < nb; ++r, kr += dim, qr += dim, mine += parts * 32) {
+                const float vv = vs[r * 32 + lane];
+                float op = 0.0f;
+#pragma unroll
+                for (int i = 0; i < PART; ++i) {
+                    if ((uint32_t)i < cnt) {
+                        const float s2 = fmaf(kr[i], vv, decay * S[i]);
+                        S[i] = s2;
+                        op = fmaf(s2, qr[i], op);
+                    }
+                }
+                *mine = op;
+            }
         }
         __syncthreads();
         for (uint32_t i = tid; i < nb * 32; i += blockDim.x) {
@@ -141,7 +189,7 @@ __global__ void __launch_bounds__(1024) retention_kernel(const uzu_retention_arg
             if (cc < vdim) out[(size_t)(tb + r) * a.out_stride + cc] = o;
         }
         // the next batch overwrites qs / ks / vs only after every thread has passed the barrier above, and `part` only after the
-        // barrier that follows its staging loop
+        // barrier that follows its staging stores
     }
 #pragma unroll
     for (int i = 0; i < PART; ++i)
@@ -186,7 +234,7 @@ void uzu_retention_encode(uzu_command_buffer* cmd, const uzu_retention_args* a) 
     int part = 4;
     while (part * 16 < (int)b.dim) part *= 2;
     while ((b.dim + part - 1) / part > 32) part *= 2;
-    const uint32_t parts = (b.dim + part - 1) / part;
+    const uint32_t parts = std::max(4u, (b.dim + part - 1) / part);      // at least 4 warps stage a batch (warps past the last key channel only help there)
     const size_t smem = ((size_t)2 * RT_BATCH * b.dim + (size_t)RT_BATCH * 32 + (size_t)RT_BATCH * parts * 32) * sizeof(float);
     const dim3 grid((b.vdim + 31) / 32, b.heads), block(parts * 32);
     // the opt-in is made once per instance and device: for the longest keys the instance serves (32 warps of `part` channels)

@@ -132,6 +132,40 @@ __device__ void route_sort_pairs(const uint16_t* pe, uint32_t* counts, uint32_t 
     // Stable placement, counts[e] now being the next free position of expert e: pairs are taken in chunks of one per thread, the warps of
     // a chunk one after the other; within a warp the lanes that hold the same expert are ranked by lane and their leader moves the cursor.
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    // Few experts: every warp of a chunk counts its pairs per expert at once, one thread per expert turns the counts into the warps' start
+    // positions (in warp order), then every pair is placed: four barriers per chunk instead of one per warp.
+    constexpr uint32_t kFew = 64;
+    __shared__ uint32_t warp_start[32][kFew];
+    if (experts <= kFew && warps <= 32) {
+        for (uint32_t base = 0; base < pairs; base += blockDim.x) {
+            for (uint32_t i = threadIdx.x; i < 32 * kFew; i += blockDim.x) (&warp_start[0][0])[i] = 0;
+            __syncthreads();
+            const uint32_t p = base + threadIdx.x;
+            const bool valid = p < pairs;
+            const uint32_t e = valid ? pe[p] : 0x10000u + lane;
+            const uint32_t same = __match_any_sync(0xffffffffu, e);
+            const uint32_t rank = __popc(same & ((1u << lane) - 1u));
+            if (valid && rank == 0) warp_start[warp][e] = __popc(same);
+            __syncthreads();
+            if (threadIdx.x < experts) {
+                uint32_t cur = counts[threadIdx.x];
+                for (uint32_t w = 0; w < warps; ++w) {
+                    const uint32_t c = warp_start[w][threadIdx.x];
+                    warp_start[w][threadIdx.x] = cur;
+                    cur += c;
+                }
+                counts[threadIdx.x] = cur;
+            }
+            __syncthreads();
+            if (valid) {
+                const uint32_t at = warp_start[warp][e] + rank;
+                rows_map[at] = p / top;
+                pair_pos[p] = at;
+            }
+            __syncthreads();
+        }
+        return;
+    }
     for (uint32_t base = 0; base < pairs; base += blockDim.x) {
         const uint32_t p = base + threadIdx.x;
         const bool valid = p < pairs;
