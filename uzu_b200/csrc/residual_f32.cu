@@ -136,7 +136,7 @@ __device__ void route_sort_pairs(const uint16_t* pe, uint32_t* counts, uint32_t 
     // positions (in warp order), then every pair is placed: four barriers per chunk instead of one per warp.
     constexpr uint32_t kFew = 64;
     __shared__ uint32_t warp_start[32][kFew];
-    if (experts <= kFew && warps <= 32) {
+    if (experts <= kFew && warps <= 32 && pairs > 32) {        // (a single warp's worth of pairs takes the loop below in one step)
         for (uint32_t base = 0; base < pairs; base += blockDim.x) {
             for (uint32_t i = threadIdx.x; i < 32 * kFew; i += blockDim.x) (&warp_start[0][0])[i] = 0;
             __syncthreads();
