@@ -45,7 +45,7 @@ def close(got, ref, tol, what=""):
 
 
 # ---- kernels, one mechanism each ---------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("rows,n", [(1, 37), (5, 224), (8, 70), (64, 96), (300, 33), (1024, 130)])
+@pytest.mark.parametrize("rows,n", [(1, 37), (5, 200), (8, 70), (64, 96), (300, 33), (1024, 130)])
 def test_min_gru_scan_one_launch_and_carried_state(ctx, rows, n):
     """Strided operands inside a wider block; the launch over all rows (chunks composed in order) and the same rows in two launches with the
     state carried both equal the token-by-token scan."""
@@ -77,13 +77,13 @@ def test_min_gru_candidate_branches_and_saturated_gates(ctx):
     close(bo.numpy(np.float32, (1, 5)), [[0.5, 7.0, 0.75, 2.0, 0.0]], 1e-6, "branches")
 
 
-@pytest.mark.parametrize("rows,heads,dim,vdim", [(1, 3, 64, 32), (17, 2, 9, 7), (100, 2, 128, 64), (40, 1, 48, 96), (33, 5, 20, 33)])
+@pytest.mark.parametrize("rows,heads,dim,vdim", [(1, 3, 64, 48), (17, 2, 9, 7), (100, 2, 128, 64), (40, 1, 48, 96), (33, 5, 20, 33)])
 def test_retention_state_and_outputs(ctx, rows, heads, dim, vdim):
     """Decays of 1 (nothing forgotten), 1/2 and close to 1; key size != value size; one launch equals two launches with the state carried."""
     rng = np.random.default_rng(rows + dim)
     ld = heads * (2 * dim + vdim) + 3
     block = rng.standard_normal((rows, ld)).astype(np.float32)
-    decay = np.array(([1.0, 0.5, 0.984375, 0.75, 0.999])[:heads], np.float32)
+    decay = np.array(([1.0, 0.5, 0.96875, 0.75, 0.999])[:heads], np.float32)
     s0 = rng.standard_normal((heads, dim, vdim)).astype(np.float32)
     q = t64(block[:, :heads * dim]).reshape(rows, heads, dim)
     k = t64(block[:, heads * dim:2 * heads * dim]).reshape(rows, heads, dim)
@@ -134,7 +134,7 @@ def test_head_norm_with_silu_gate(ctx):
     close(bo.numpy(np.float32, x.shape), ref.numpy(), 3e-6, "unit rms * silu(gate)")
 
 
-@pytest.mark.parametrize("rows,experts,top", [(1, 16, 1), (7, 5, 5), (40, 6, 2), (300, 9, 3)])
+@pytest.mark.parametrize("rows,experts,top", [(1, 12, 1), (7, 5, 5), (40, 6, 2), (300, 9, 3)])
 @pytest.mark.parametrize("f32_weights", [True, False])
 def test_sigmoid_router_weights_scale_the_expert_input(ctx, rows, experts, top, f32_weights):
     """Router: the `top` largest logits, weight = sigmoid of each on its own. The gate / up product of a pair is multiplied by the pair's weight
@@ -251,9 +251,9 @@ def new_cache(ctx, positions, kv_heads, dim, vdim, f32_cache):
 
 
 @pytest.mark.parametrize("T,prefix,heads,kv_heads,dim,vdim,rot_dims,window,keep", [
-    (40, 0, 4, 2, 16, 24, 16, 7, 2), (9, 31, 6, 3, 48, 96, 48, 20, 4), (70, 5, 2, 2, 10, 6, 4, 16, 0), (33, 0, 3, 1, 64, 32, 32, 1, 3),
+    (40, 0, 4, 2, 16, 24, 16, 7, 2), (9, 31, 6, 2, 48, 80, 48, 20, 5), (70, 5, 2, 2, 10, 6, 4, 16, 0), (33, 0, 3, 1, 64, 32, 32, 1, 3),
     (130, 20, 2, 1, 128, 128, 64, 50, 1), (20, 0, 1, 1, 9, 14, 8, 0, 0), (25, 40, 2, 2, 24, 8, 24, 100, 5), (12, 3, 2, 1, 300, 40, 300, 6, 6),
-    (200, 0, 4, 2, 64, 32, 64, 70, 3), (150, 37, 2, 1, 48, 96, 48, 20, 4), (300, 100, 2, 2, 16, 16, 8, 0, 0), (260, 0, 1, 1, 32, 64, 32, 1, 70),
+    (200, 0, 4, 2, 64, 32, 64, 70, 3), (150, 37, 2, 1, 48, 80, 32, 20, 3), (300, 100, 2, 2, 16, 16, 8, 0, 0), (260, 0, 1, 1, 32, 64, 32, 1, 70),
     (70, 700, 2, 1, 64, 64, 64, 128, 5), (64, 1, 2, 2, 16, 112, 16, 63, 65)])
 @pytest.mark.parametrize("f32_cache", [True, False])
 def test_window_attention_kernels(ctx, T, prefix, heads, kv_heads, dim, vdim, rot_dims, window, keep, f32_cache):

@@ -548,7 +548,7 @@ def vugipel_parallel_layer(heads: int, kv_heads: int, dim: int, vdim: int, windo
             "softcap": float(softcap), "rot": {"base": float(rot_base), "dims": int(rot_dims if rot_dims is not None else dim)},
             "mask": {"size": int(window), "keep_first": int(keep_first)}}
     if decay is None:
-        decay = [1.0 - 2.0 ** -(5 + (h % 6)) for h in range(r_heads)]
+        decay = [1.0 - 1.0 / (24.0 * (h % 8 + 1)) for h in range(r_heads)]
     right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": [float(d) for d in decay]}
     return {"type": "parallel", "mixer": {"left": left, "left_scale": float(left_scale), "right": right, "right_scale": float(right_scale)}, "mlp": mlp}
 
