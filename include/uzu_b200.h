@@ -540,6 +540,7 @@ typedef struct uzu_topk_route_args {
     uint32_t weight_kind;          /* 0: softmax over the chosen logits; 1: sigmoid of each chosen logit on its own (not renormalised) */
     uint32_t reserved;
     uint64_t compact_weight;       /* optional f32 [rows*top]: the same weights in the compact (expert-sorted) order of rows_map */
+    uint64_t scratch;              /* optional u16 [rows*top]: with it, passes of >= 64 rows make the choice over many CTAs (a second launch sorts) */
 } uzu_topk_route_args;
 UZU_API void uzu_topk_route_encode(uzu_command_buffer* cmd, const uzu_topk_route_args* args);
 

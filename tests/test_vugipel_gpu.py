@@ -147,13 +147,18 @@ def test_sigmoid_router_weights_scale_the_expert_input(ctx, rows, experts, top, 
     bz = ctx.upload(z)
     off, rmap, ppos = ctx.upload(np.zeros(experts + 1, np.uint32)), ctx.upload(np.zeros(rows * top, np.uint32)), ctx.upload(np.zeros(rows * top, np.uint32))
     pw, cw = ctx.upload(np.zeros(rows * top, np.float32)), ctx.upload(np.zeros(rows * top, np.float32))
+    scratch = ctx.upload(np.zeros(rows * top, np.uint16))          # with it, the 300-row case makes its choice over many CTAs
     ra = B.TopkRouteArgs(logits=bz.ptr, bias=0, group_offsets=off.ptr, rows_map=rmap.ptr, pair_pos=ppos.ptr, pair_weight=pw.ptr, rows=rows, top=top,
-                         experts=experts, logits_stride=experts, weight_kind=1, compact_weight=cw.ptr)
+                         experts=experts, logits_stride=experts, weight_kind=1, compact_weight=cw.ptr, scratch=scratch.ptr)
     run(ctx, "uzu_topk_route_encode", C.byref(ra))
     pos, weights, compact = ppos.numpy(np.uint32, (rows, top)), pw.numpy(np.float32, (rows, top)), cw.numpy(np.float32, (rows * top,))
     order = np.argsort(-z, axis=1, kind="stable")[:, :top]
     close(weights, 1.0 / (1.0 + np.exp(-np.take_along_axis(z.astype(np.float64), order, 1))), 2e-6, "sigmoid weights, largest first")
     np.testing.assert_array_equal(compact[pos.reshape(-1)], weights.reshape(-1))
+    offsets, rows_of = off.numpy(np.uint32, (experts + 1,)), rmap.numpy(np.uint32, (rows * top,))
+    for e in range(experts):                                       # the pairs of an expert, in token order
+        want = [r for r in range(rows) if e in order[r]]
+        assert rows_of[offsets[e]:offsets[e + 1]].tolist() == want, f"expert {e}"
     bh, bw = ctx.upload(h), ctx.upload(gu if f32_weights else synth.f32_to_bf16_bits(gu))
     paired = rows <= 8
     bd = ctx.upload(np.zeros((rows * top, f if paired else 2 * f), np.float32))

@@ -169,7 +169,7 @@ LatentAttentionArgs = _struct("uzu_latent_attention_args", [
 
 TopkRouteArgs = _struct("uzu_topk_route_args", [
     ("logits", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64), ("pair_pos", u64), ("pair_weight", u64),
-    ("rows", u32), ("top", u32), ("experts", u32), ("logits_stride", u32), ("weight_kind", u32), ("reserved", u32), ("compact_weight", u64)])
+    ("rows", u32), ("top", u32), ("experts", u32), ("logits_stride", u32), ("weight_kind", u32), ("reserved", u32), ("compact_weight", u64), ("scratch", u64)])
 
 RoutedCombineArgs = _struct("uzu_routed_combine_args", [
     ("pairs", u64), ("pair_pos", u64), ("pair_weight", u64), ("gate", u64), ("gate_bias", u64), ("col_scale", u64), ("output", u64),

@@ -508,6 +508,7 @@ struct uzu_engine {
     struct PbScratch {
         Buf normed2, proj2, pair_weight, attn_tickets;   // second normed copy, the feed-forward's router / gate logits, router weights, split tickets
         Buf pair_weight_compact;                         // router weights in the expert-sorted order of the pair list
+        Buf route_scratch;                               // the experts a long pass picked, between the router's two launches
         Buf resid, normed, operand_bf16, proj, lat, wide, lat_wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;

@@ -682,6 +682,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     P.proj2 = dev(R * proj2 * 4);
     P.pair_weight = dev(R * top * 4);
     P.pair_weight_compact = dev(R * top * 4);
+    P.route_scratch = dev(R * top * 2);
     P.attn_tickets = dev((size_t)kSplitRows * tickets * 4);
     cudaMemset((void*)P.attn_tickets.ptr(), 0, (size_t)kSplitRows * tickets * 4);
     P.operand_bf16 = dev(R * kmax * 2);     // bf16 copy of a prompt pass's activation rows for the tensor-memory products
@@ -980,6 +981,7 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
         ra.pair_pos = P.pair_pos.ptr(); ra.pair_weight = P.pair_weight.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts;
         ra.logits_stride = M.router.rows;
         ra.weight_kind = M.sigmoid_weights ? 1 : 0;
+        ra.scratch = P.route_scratch.ptr();
         if (M.weight_on_input) ra.compact_weight = P.pair_weight_compact.ptr();
         if (!M.router_bias.b) ra.bias = 0;
         uzu_topk_route_encode(cmd, &ra);

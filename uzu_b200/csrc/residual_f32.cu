@@ -121,7 +121,13 @@ __device__ void route_sort_pairs(const uint16_t* pe, uint32_t* counts, uint32_t 
                                  uint32_t* rows_map, uint32_t* pair_pos) {
     for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[pe[p] + 1], 1u);
+    for (uint32_t base = 0; base < pairs; base += blockDim.x) {      // one shared-memory add per (warp, expert): lanes with the same expert elect a leader
+        const uint32_t p = base + threadIdx.x;
+        const bool valid = p < pairs;
+        const uint32_t e = valid ? pe[p] : 0x10000u + (threadIdx.x & 31);
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        if (valid && (threadIdx.x & 31) == (uint32_t)(__ffs(same) - 1)) atomicAdd(&counts[e + 1], (uint32_t)__popc(same));
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         for (uint32_t e = 0; e < experts; ++e) counts[e + 1] += counts[e];
@@ -213,17 +219,32 @@ __global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route
 // One CTA, a warp per row: `top` rounds, each picking the best (logit, lower index first) that comes after the previous pick in that
 // order, so no list of the picked experts is kept. Weights: exp(z - z_first) over the sum of the picked ones, or (weight_kind 1) the
 // sigmoid of every picked logit on its own. compact_weight gets the same weights in the expert-sorted order of the pair list.
+// MODE 0: choice and pair lists in one CTA (short passes). Long passes with a scratch: MODE 1 makes the choice over many CTAs (a warp per
+// row, the picked experts go to the scratch), MODE 2 is the one CTA that sorts them into the pair lists.
+template <int MODE>
 __global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_args a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ uint32_t counts[];   // [experts + 1]
     const uint32_t pairs = a.rows * a.top;
-    uint16_t* pe = reinterpret_cast<uint16_t*>(counts + a.experts + 1);
+    uint16_t* pe_shared = reinterpret_cast<uint16_t*>(counts + a.experts + 1);
+    uint16_t* pe = MODE == 1 ? reinterpret_cast<uint16_t*>(a.scratch) : pe_shared;
     const float* bias = reinterpret_cast<const float*>(a.bias);
     float* weight = reinterpret_cast<float*>(a.pair_weight);
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const uint32_t lane = threadIdx.x & 31, warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), warps = gridDim.x * (blockDim.x >> 5);
+    if constexpr (MODE == 2) {
+        const uint16_t* chosen = reinterpret_cast<const uint16_t*>(a.scratch);
+        for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) pe_shared[p] = chosen[p];
+    } else {
+    // a lane keeps the logit of expert `lane` of its row in a register for all rounds, and requests the next row's before it works on this one
+    auto first_logit = [&](uint32_t r) {
+        return (r < a.rows && lane < a.experts) ? reinterpret_cast<const float*>(a.logits)[(size_t)r * a.logits_stride + lane] + (bias ? bias[lane] : 0.0f) : 0.0f;
+    };
+    float next_z = first_logit(warp);
     for (uint32_t r = warp; r < a.rows; r += warps) {
         const float* z = reinterpret_cast<const float*>(a.logits) + (size_t)r * a.logits_stride;
+        const float own_z = next_z;
+        next_z = first_logit(r + warps);
         float prev_v = INFINITY, first = 0.0f, sum = 0.0f;
         uint32_t prev_i = 0;
         bool any = false;
@@ -231,7 +252,7 @@ __global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_a
             float best_v = -INFINITY;
             uint32_t best_i = 0xFFFFFFFFu;
             for (uint32_t e = lane; e < a.experts; e += 32) {
-                const float v = z[e] + (bias ? bias[e] : 0.0f);
+                const float v = e == lane ? own_z : z[e] + (bias ? bias[e] : 0.0f);
                 const bool after = !any || v < prev_v || (v == prev_v && e > prev_i);
                 if (after && (best_i == 0xFFFFFFFFu || v > best_v)) { best_v = v; best_i = e; }    // ascending e: the first of equals stays
             }
@@ -257,8 +278,10 @@ __global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_a
             for (uint32_t s = lane; s < a.top; s += 32) weight[r * a.top + s] /= sum;
         }
     }
+    }
+    if constexpr (MODE == 1) return;
     __syncthreads();
-    route_sort_pairs(pe, counts, pairs, a.top, a.experts, reinterpret_cast<uint32_t*>(a.group_offsets), reinterpret_cast<uint32_t*>(a.rows_map),
+    route_sort_pairs(pe_shared, counts, pairs, a.top, a.experts, reinterpret_cast<uint32_t*>(a.group_offsets), reinterpret_cast<uint32_t*>(a.rows_map),
                      reinterpret_cast<uint32_t*>(a.pair_pos));
     if (a.compact_weight) {
         __syncthreads();
@@ -377,7 +400,12 @@ void uzu_topk_route_encode(uzu_command_buffer* cmd, const uzu_topk_route_args* a
         cmd->record_error(UZU_ERROR_UNSUPPORTED, "topk_route: rows * top too large for one pass");
         return;
     }
-    launch(cmd, "topk_route_kernel", topk_route_kernel, dim3(1), dim3(1024), smem, *a);
+    if (a->scratch && a->rows >= 64) {          // the choice over many CTAs (8 rows each), then the one CTA that builds the lists
+        launch(cmd, "topk_route_kernel", topk_route_kernel<1>, dim3((a->rows + 7) / 8), dim3(256), 0, *a);
+        launch(cmd, "topk_route_kernel", topk_route_kernel<2>, dim3(1), dim3(1024), smem, *a);
+        return;
+    }
+    launch(cmd, "topk_route_kernel", topk_route_kernel<0>, dim3(1), dim3(1024), smem, *a);
 }
 
 void uzu_routed_combine_gated_encode(uzu_command_buffer* cmd, const uzu_routed_combine_args* a) {
