@@ -503,6 +503,29 @@ typedef struct uzu_group_rms_norm_args {
 } uzu_group_rms_norm_args;
 UZU_API void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_rms_norm_args* args);
 
+/* A norm of `input`, optionally added into a residual stream, optionally followed by the next sublayer's norm of the updated stream:
+ *   norm(x)  = x / sqrt(mean(x^2) + epsilon) * weight (+ bias)          (kind 0: RMS norm)
+ *            = tanh(alpha * x) * weight + bias                          (kind 1: Dynamic Tanh, no mean and no variance)
+ *   residual == 0:  output = norm(input)
+ *   residual != 0:  residual += mult * norm(input);  output (optional) = next_norm(residual), of kind next_kind with next_weight /
+ *                   next_bias / next_alpha.
+ * All f32; rows of `n` elements (input rows `in_stride` apart, residual and output rows dense); weight and bias optional (1 and 0). */
+typedef struct uzu_norm_add_args {
+    uint64_t input, weight, bias, residual, output, next_weight, next_bias;
+    uint32_t rows, n, in_stride, kind, next_kind;
+    float alpha, epsilon, mult, next_alpha;
+    uint32_t reserved;
+} uzu_norm_add_args;
+UZU_API void uzu_norm_add_encode(uzu_command_buffer* cmd, const uzu_norm_add_args* args);
+
+/* Per-layer token input, the elementwise part: out[r, i] = gelu_tanh(z[r, i]) * table[token[r], column + i] for i < n, with
+ * gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); table is weights_dt [vocab, table_stride]; z, out f32 [rows, n]. */
+typedef struct uzu_token_gate_args {
+    uint64_t z, token_ids, table, out;
+    uint32_t rows, n, vocab, table_stride, column, weights_dt;
+} uzu_token_gate_args;
+UZU_API void uzu_token_gate_encode(uzu_command_buffer* cmd, const uzu_token_gate_args* args);
+
 /* Elementwise glue, all f32.
  *   embedding_f32:   out[r, :] = table[token[r], :] (table weights_dt [vocab, n])
  *   clamped_glu:     g = min(gate, limit); u = clamp(up, -limit, limit); out = g * sigmoid(alpha * g) * (u + 1); gate / up are column
@@ -512,6 +535,9 @@ UZU_API void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_
  *   logit_cap_f32:   l = cap * tanh(l / cap) (has_cap), and a bf16 copy for the sampling kernels */
 UZU_API void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output,
                                       uint32_t rows, uint32_t vocab, uint32_t n);
+/*   embedding_f32_scaled: the same rows times `scale` */
+UZU_API void uzu_embedding_f32_scaled_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output,
+                                             uint32_t rows, uint32_t vocab, uint32_t n, float scale);
 UZU_API void uzu_clamped_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f, float limit, float alpha);
 /*   silu_glu:        out = g * sigmoid(g) * u, same operand layout as clamped_glu */
 UZU_API void uzu_silu_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f);
@@ -600,12 +626,16 @@ typedef struct uzu_general_delta_args {
 UZU_API void uzu_general_delta_encode(uzu_command_buffer* cmd, const uzu_general_delta_args* args);
 
 /* out[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + epsilon) * scales[h*dim + :] * act(gate[r, h*dim + :]); scales / gate optional;
- * act = sigmoid (gate_op 0) or silu (gate_op 1) */
+ * act = sigmoid (gate_op 0) or silu (gate_op 1). With `denom` (f32 [rows, heads]) the head's row is first divided by
+ * max(|denom[r, h]|, denom_floor[r, h]) + denom_epsilon (a linear memory's normaliser; denom_floor optional). */
 typedef struct uzu_head_norm_gate_args {
     uint64_t x, scales, gate, out;
     uint32_t rows, heads, dim, x_stride, gate_stride, out_stride, normalize;
     float epsilon;
     uint32_t gate_op, reserved;
+    uint64_t denom, denom_floor;
+    float denom_epsilon;
+    uint32_t reserved1;
 } uzu_head_norm_gate_args;
 UZU_API void uzu_head_norm_gate_encode(uzu_command_buffer* cmd, const uzu_head_norm_gate_args* args);
 
@@ -624,13 +654,18 @@ typedef struct uzu_latent_prepare_args {
 UZU_API void uzu_latent_prepare_encode(uzu_command_buffer* cmd, const uzu_latent_prepare_args* args);
 
 /* Causal softmax attention of `rows` queries over the latent cache shared by all heads: score(t, h, j) = scale * query[t,h,:] .
- * cache[j,:] for j <= prefix + t, out[t, h, :] = sum_j softmax_j * cache[j, 0:rank]  (f32 [rows, heads, rank]). */
+ * cache[j,:] for j <= p = prefix + t (and p - j < window, if any), out[t, h, :] = sum_j softmax_j * cache[j, 0:rank]
+ * (f32 [rows, heads, rank]); optional sink term in the denominator and sigmoid gate per head. */
 typedef struct uzu_latent_attention_args {
     uint64_t query, cache, out, dynamic_position;
     uint64_t partials;             /* scratch f32 [rows, heads, splits, rank + 2] when splits > 1 */
     uint32_t rows, heads, rank, rot_dim, prefix, cache_dt;
     float scale;
-    uint32_t splits;               /* the causal key range of every query is cut into this many parts, one CTA each (0 / 1 = none) */
+    uint32_t splits;               /* the visible key range of every query is cut into this many parts, one CTA each (0 / 1 = none) */
+    uint64_t sinks;                /* optional f32 [heads]: the softmax denominator also holds exp(sinks[h]) (no key, no value, not scaled) */
+    uint64_t head_gate;            /* optional f32 [rows, head_gate_stride]: head h's output is multiplied by sigmoid(head_gate[t, h]) */
+    uint32_t window;               /* > 0: only keys j with p - j < window are visible (the query's own position and window - 1 before it) */
+    uint32_t head_gate_stride;
 } uzu_latent_attention_args;
 UZU_API void uzu_latent_attention_encode(uzu_command_buffer* cmd, const uzu_latent_attention_args* args);
 
@@ -653,12 +688,35 @@ typedef struct uzu_retention_args {
     uint32_t rows, heads, dim, vdim, q_stride, k_stride, v_stride, out_stride;
     float key_scale;
     uint32_t reserved;
+    /* Gated form (token_decay != 0; `decay` is then unused): the factors change from token to token,
+     *   S_t = token_decay[t, h] * S_(t-1) + token_gain[t, h] * (key_scale * k_t) v_t^T,   out[t, h, :] = S_t^T (query_scale * q_t)
+     * and, with norm_out, a normaliser n_t = token_decay n_(t-1) + token_gain * key_scale * k_t is kept as one more state column:
+     * the state is then f32 [heads, dim, vdim + 1] and norm_out[t, h] = n_t . (query_scale * q_t). */
+    uint64_t token_decay, token_gain;      /* f32 [rows, heads] */
+    uint64_t norm_out;                     /* optional f32 [rows, heads] */
+    float query_scale;                     /* 0 = 1 */
+    uint32_t reserved1;
 } uzu_retention_args;
 UZU_API void uzu_retention_encode(uzu_command_buffer* cmd, const uzu_retention_args* args);
 
+/* Exponential gates of a matrix memory with a running maximum (mLSTM), for `rows` tokens of one sequence in token order. Per head, from
+ * the biased projections i_pre, f_pre:  i = cap * tanh(i_pre / cap),  f = logsigmoid(cap * tanh(f_pre / cap))  (cap = 0: no cap),
+ *   m_t = max(f + m_(t-1), i);  token_decay = exp(f + m_(t-1) - m_t);  token_gain = exp(i - m_t);  floor = exp(-m_t)
+ * m is read from and written back to `state` (f32 [heads]; a new sequence starts at 0). All f32. */
+typedef struct uzu_exp_gates_args {
+    uint64_t i_pre, f_pre;                 /* f32 [rows, stride] */
+    uint64_t state;                        /* f32 [heads] */
+    uint64_t token_decay, token_gain, floor;   /* f32 [rows, heads] */
+    uint32_t rows, heads, i_stride, f_stride;
+    float cap;
+    uint32_t reserved;
+} uzu_exp_gates_args;
+UZU_API void uzu_exp_gates_encode(uzu_command_buffer* cmd, const uzu_exp_gates_args* args);
+
 /* Windowed softmax attention, cache side and query side of one pass. Per token row t at position p = prefix + t (prefix read from
  * dynamic_position when non-zero), per head: optional RMS norm over the head's `dim` channels times q_scales / k_scales [dim] (shared by
- * all heads), then interleaved-pair rotation of the first 2 * rot_pairs channels by cos / sin rows [positions, rot_pairs]:
+ * all heads), then rotation of the first 2 * rot_pairs channels (interleaved pairs, or two halves with rot_halves) by cos / sin rows
+ * [positions, rot_pairs]:
  *   query[t, h, :] = rotate_p(norm(q[t, h, :]))             (f32 [rows, heads*dim])
  *   keys[p, g, :]  = rotate_p(norm(k[t, g, :]))             (cache_dt [positions, kv_heads*dim])
  *   values[p, g, :] = rotate_p(v[t, g, :]) over 2 * v_pairs channels by their own cos / sin rows (v_pairs = 0: stored as they are) */
@@ -666,7 +724,7 @@ typedef struct uzu_window_attention_prepare_args {
     uint64_t q, k, v, q_scales, k_scales, query, keys, values, cosines, sines, v_cosines, v_sines, dynamic_position;
     uint32_t rows, heads, kv_heads, dim, vdim, rot_pairs, v_pairs, q_stride, k_stride, v_stride, prefix, cache_dt;
     float epsilon;
-    uint32_t reserved;
+    uint32_t rot_halves;           /* 1: q / k pair channel i with channel i + rot_pairs (two halves) instead of (2i, 2i + 1); values keep the interleaved pairs */
 } uzu_window_attention_prepare_args;
 UZU_API void uzu_window_attention_prepare_encode(uzu_command_buffer* cmd, const uzu_window_attention_prepare_args* args);
 

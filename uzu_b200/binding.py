@@ -155,7 +155,7 @@ GeneralDeltaArgs = _struct("uzu_general_delta_args", [
 HeadNormGateArgs = _struct("uzu_head_norm_gate_args", [
     ("x", u64), ("scales", u64), ("gate", u64), ("out", u64),
     ("rows", u32), ("heads", u32), ("dim", u32), ("x_stride", u32), ("gate_stride", u32), ("out_stride", u32), ("normalize", u32),
-    ("epsilon", f32), ("gate_op", u32), ("reserved", u32)])
+    ("epsilon", f32), ("gate_op", u32), ("reserved", u32), ("denom", u64), ("denom_floor", u64), ("denom_epsilon", f32), ("reserved1", u32)])
 
 LatentPrepareArgs = _struct("uzu_latent_prepare_args", [
     ("kv", u64), ("q", u64), ("query", u64), ("cache", u64), ("latent_scales", u64), ("cosines", u64), ("sines", u64),
@@ -165,7 +165,8 @@ LatentPrepareArgs = _struct("uzu_latent_prepare_args", [
 
 LatentAttentionArgs = _struct("uzu_latent_attention_args", [
     ("query", u64), ("cache", u64), ("out", u64), ("dynamic_position", u64), ("partials", u64),
-    ("rows", u32), ("heads", u32), ("rank", u32), ("rot_dim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32), ("splits", u32)])
+    ("rows", u32), ("heads", u32), ("rank", u32), ("rot_dim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32), ("splits", u32),
+    ("sinks", u64), ("head_gate", u64), ("window", u32), ("head_gate_stride", u32)])
 
 TopkRouteArgs = _struct("uzu_topk_route_args", [
     ("logits", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64), ("pair_pos", u64), ("pair_weight", u64),
@@ -194,13 +195,26 @@ MinGruArgs = _struct("uzu_min_gru_args", [
 RetentionArgs = _struct("uzu_retention_args", [
     ("q", u64), ("k", u64), ("v", u64), ("decay", u64), ("state", u64), ("out", u64),
     ("rows", u32), ("heads", u32), ("dim", u32), ("vdim", u32), ("q_stride", u32), ("k_stride", u32), ("v_stride", u32), ("out_stride", u32),
-    ("key_scale", f32), ("reserved", u32)])
+    ("key_scale", f32), ("reserved", u32), ("token_decay", u64), ("token_gain", u64), ("norm_out", u64), ("query_scale", f32), ("reserved1", u32)])
+
+ExpGatesArgs = _struct("uzu_exp_gates_args", [
+    ("i_pre", u64), ("f_pre", u64), ("state", u64), ("token_decay", u64), ("token_gain", u64), ("floor", u64),
+    ("rows", u32), ("heads", u32), ("i_stride", u32), ("f_stride", u32), ("cap", f32), ("reserved", u32)])
+
+NormAddArgs = _struct("uzu_norm_add_args", [
+    ("input", u64), ("weight", u64), ("bias", u64), ("residual", u64), ("output", u64), ("next_weight", u64), ("next_bias", u64),
+    ("rows", u32), ("n", u32), ("in_stride", u32), ("kind", u32), ("next_kind", u32),
+    ("alpha", f32), ("epsilon", f32), ("mult", f32), ("next_alpha", f32), ("reserved", u32)])
+
+TokenGateArgs = _struct("uzu_token_gate_args", [
+    ("z", u64), ("token_ids", u64), ("table", u64), ("out", u64),
+    ("rows", u32), ("n", u32), ("vocab", u32), ("table_stride", u32), ("column", u32), ("weights_dt", u32)])
 
 WindowAttentionPrepareArgs = _struct("uzu_window_attention_prepare_args", [
     ("q", u64), ("k", u64), ("v", u64), ("q_scales", u64), ("k_scales", u64), ("query", u64), ("keys", u64), ("values", u64),
     ("cosines", u64), ("sines", u64), ("v_cosines", u64), ("v_sines", u64), ("dynamic_position", u64),
     ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("rot_pairs", u32), ("v_pairs", u32),
-    ("q_stride", u32), ("k_stride", u32), ("v_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("reserved", u32)])
+    ("q_stride", u32), ("k_stride", u32), ("v_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("rot_halves", u32)])
 
 WindowAttentionArgs = _struct("uzu_window_attention_args", [
     ("query", u64), ("keys", u64), ("values", u64), ("out", u64), ("dynamic_position", u64), ("head_temp", u64),
@@ -210,7 +224,7 @@ WindowAttentionArgs = _struct("uzu_window_attention_args", [
 
 MAIN_SLOT = 0xFFFFFFFF
 
-ABI_STRUCTS = [MinGruArgs, RetentionArgs, WindowAttentionPrepareArgs, WindowAttentionArgs, TopkRouteArgs, RoutedCombineArgs, SigmoidAttentionPrepareArgs, SigmoidAttentionArgs, DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
+ABI_STRUCTS = [ExpGatesArgs, NormAddArgs, TokenGateArgs, MinGruArgs, RetentionArgs, WindowAttentionPrepareArgs, WindowAttentionArgs, TopkRouteArgs, RoutedCombineArgs, SigmoidAttentionPrepareArgs, SigmoidAttentionArgs, DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
                DeltaNetFusedUpdateArgs, QkNormConfig, AttentionPrepareNormArgs, FusedLinearArgs, RingParams, TrieNode, KvCopy, MatmulArgs, NormalizationArgs, QkvNormArgs, AttentionPrepareArgs, AttentionArgs,
                AttentionTwoPass2Args, KvCacheUpdateArgs, GatedActMulArgs, QuantizedEmbeddingLookupArgs, UnifiedSamplingArgs,
                DeltaNetConvUpdateArgs, DeltaNetUpdateArgs, EngineOptions, SamplingMethod, ModelInfo, TpAllGatherArgs]
@@ -243,7 +257,8 @@ uzu_unary_f32_encode uzu_residual_add_encode uzu_logit_cap_f32_encode uzu_table_
 uzu_general_delta_encode uzu_head_norm_gate_encode uzu_latent_prepare_encode uzu_latent_attention_encode
 uzu_silu_glu_encode uzu_topk_route_encode uzu_routed_combine_gated_encode uzu_sigmoid_attention_prepare_encode uzu_sigmoid_attention_encode
 uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs uzu_debug_dense_umma_error
-uzu_min_gru_encode uzu_retention_encode uzu_window_attention_prepare_encode uzu_window_attention_encode""".split()
+uzu_min_gru_encode uzu_retention_encode uzu_window_attention_prepare_encode uzu_window_attention_encode
+uzu_exp_gates_encode uzu_norm_add_encode uzu_token_gate_encode uzu_embedding_f32_scaled_encode""".split()
 
 _lib = None
 
@@ -398,6 +413,10 @@ def load() -> C.CDLL:
         "uzu_retention_encode": (None, [vp, C.POINTER(RetentionArgs)]),
         "uzu_window_attention_prepare_encode": (None, [vp, C.POINTER(WindowAttentionPrepareArgs)]),
         "uzu_window_attention_encode": (None, [vp, C.POINTER(WindowAttentionArgs)]),
+        "uzu_exp_gates_encode": (None, [vp, C.POINTER(ExpGatesArgs)]),
+        "uzu_norm_add_encode": (None, [vp, C.POINTER(NormAddArgs)]),
+        "uzu_token_gate_encode": (None, [vp, C.POINTER(TokenGateArgs)]),
+        "uzu_embedding_f32_scaled_encode": (None, [vp, u64, u64, u32, u64, u32, u32, u32, f32]),
         "uzu_engine_slot_acquire": (C.c_int, [vp, C.POINTER(u32)]),
         "uzu_engine_slot_release": (C.c_int, [vp, u32]),
         "uzu_engine_forward_rows": (C.c_int, [vp, u32, C.POINTER(u32), u32, C.POINTER(u32), u32, C.POINTER(C.c_float)]),

@@ -286,6 +286,10 @@ struct Norm {
     Buf scales;
     uint32_t n = 0;
     bool present = false;
+    // parallel-block engine: kind 1 is the Dynamic Tanh norm tanh(alpha x) * scales + bias (no mean, no variance); kind 0 the RMS norm
+    uint32_t kind = 0;
+    Buf bias;
+    float alpha = 1.0f;
 };
 
 struct RopeCfg {
@@ -336,10 +340,15 @@ struct GeneralDeltaLayer {   // generalized delta rule mixer: decay and removal 
 };
 
 struct LatentAttentionLayer {   // latent attention: normed query latent, shared normed kv latent + one rotated key part
-    DenseMatrix in;             // rows [query latent | kv latent | rotated key part | output gate]
+    DenseMatrix in;             // rows [query latent | kv latent | rotated key part | output gate]; a layer that borrows its cache has no kv rows
     DenseMatrix q_up, key_absorb /* heads x [rank, dim] = per-head key up-projection transposed */, value_up /* heads x [vdim, rank] */, out;
     Buf q_norm, latent_norm;    // f32
+    Buf sink;                   // f32 [heads] (optional): one more term exp(sink) in every softmax denominator
     uint32_t heads = 0, dim = 0, rot_dim = 0, vdim = 0, rank = 0, q_rank = 0;
+    uint32_t kv_offset = 0, gate_offset = 0;   // first column of the kv latent and of the gate in the stacked projection
+    uint32_t window = 0;        // > 0: a query sees its own position and the window - 1 before it
+    bool gate_per_head = false; // the output gate is one logit per head (otherwise one per value channel)
+    int kv_from = -1;           // >= 0: this layer reads the latent cache of that (earlier) layer and keeps none
     float scale = 1.0f;
     int rope_index = -1;
 };
@@ -361,6 +370,23 @@ struct MinGruLayer {            // minGRU mixer: gates and candidate read only t
     uint32_t width = 0;
 };
 
+struct MlstmLayer {             // matrix memory with exponential gates: per head S [dim, vdim] and a normaliser, stabilised by a running maximum
+    DenseMatrix in;             // rows [query | key | value | output gate | input-gate logit | forget-gate logit]
+    DenseMatrix out;
+    Buf in_bias;                // f32 [in.rows]: zeros but under the two gate logits
+    Buf norm_weight;            // f32 [heads * vdim]
+    uint32_t heads = 0, dim = 0, vdim = 0;
+    uint32_t q_offset = 0, k_offset = 0, v_offset = 0, gate_offset = 0, i_offset = 0, f_offset = 0;
+    float gate_cap = 0.0f;
+};
+
+struct TokenSide {              // per-layer token input: x += mult * rms(W_proj (gelu_tanh(W_gate x) * table[token, column : column + dim])) * norm
+    bool present = false;
+    DenseMatrix gate, proj;     // [dim, width], [width, dim]
+    Buf norm;                   // f32 [width]
+    uint32_t dim = 0, column = 0;
+};
+
 struct WindowAttentionLayer {   // softmax attention with a sliding window that keeps the first tokens; q / k head norms, rotated q, k AND values
     DenseMatrix out;
     Buf q_norm, k_norm;         // f32 [dim], shared by the heads (absent: no norm)
@@ -370,6 +396,7 @@ struct WindowAttentionLayer {   // softmax attention with a sliding window that 
     uint32_t q_offset = 0, k_offset = 0, v_offset = 0;   // first column of each part in the layer's stacked projection
     float scale = 1.0f, softcap = 0.0f, share = 1.0f;
     int rope_index = -1, value_rope_index = -1;          // value_rope_index < 0: values are cached as they are
+    bool rot_halves = false;    // q / k pair channel i with i + rot.dims / 2 instead of (2i, 2i + 1)
 };
 
 struct RetentionLayer {         // retention: per head S <- decay S + (k / sqrt(dim)) v^T, out = S^T q; per-head unit RMS, silu gate
@@ -400,7 +427,8 @@ struct GatedMlp {               // feed-forward: dense or routed experts; the un
 };
 
 enum MixerKind : uint32_t { MixAttention = 0, MixDeltaNet = 1, MixGeneralDelta = 2, MixLatentAttention = 3, MixSigmoidAttention = 4,
-                           MixMinGru = 5, MixWindowAttention = 6, MixRetention = 7, MixSideBySide = 8 /* window attention + retention, summed */ };
+                           MixMinGru = 5, MixWindowAttention = 6, MixRetention = 7, MixSideBySide = 8 /* window attention + retention, summed */,
+                           MixMlstm = 9 };
 
 struct Layer {
     bool is_attention = true;   // the mixer keeps a per-token cache whose length advances with the context (MixAttention, MixLatentAttention)
@@ -416,7 +444,14 @@ struct Layer {
     RetentionLayer rt;
     DenseMatrix side_in;        // MixWindowAttention / MixRetention / MixSideBySide: the stacked input projection of the layer's mixers
     Buf side_in_bias;           // f32 [side_in.rows] when any part has biases
+    MlstmLayer ml;
     bool sequential = false;    // parallel-block engine: the feed-forward reads the residual AFTER the mixer's sum, through its own norm
+    // Sandwich form of a sequential layer: every sublayer's result goes through a norm of its own before it is added, times a fixed
+    // factor: x <- x + residual_mult * post(sublayer(pre(x))). With it the sublayers write a scratch row block instead of adding into x.
+    bool sandwich = false;
+    Norm post_mixer, post_mlp;
+    float residual_mult = 1.0f;
+    TokenSide side;
     bool has_window_attention() const { return kind == MixWindowAttention || kind == MixSideBySide; }
     bool has_retention() const { return kind == MixRetention || kind == MixSideBySide; }
     SublayerGate mix_gate, mlp_gate;
@@ -503,12 +538,16 @@ struct uzu_engine {
     bool parallel_block = false;
     uint32_t store_dt = UZU_DT_BF16, norm_groups = 1;
     float norm_eps = 1e-5f;
-    DenseMatrix pb_embed, pb_head;
+    DenseMatrix pb_embed, pb_head, pb_side_embed;   // pb_side_embed: [vocab, layers * side dim], the table of the per-layer token inputs
     Buf pb_final_norm;
+    Norm pb_out_norm;           // set when the output norm is not the grouped RMS norm (kind 1: Dynamic Tanh)
     struct PbScratch {
         Buf normed2, proj2, pair_weight, attn_tickets;   // second normed copy, the feed-forward's router / gate logits, router weights, split tickets
         Buf pair_weight_compact;                         // router weights in the expert-sorted order of the pair list
         Buf route_scratch;                               // the experts a long pass picked, between the router's two launches
+        Buf sub_out;                                     // a sublayer's result before its own norm (sandwich layers)
+        Buf token_factors;                               // per (token, head) decay, gain, floor and normaliser product of a gated matrix memory
+        bool redirect = false;                           // the sublayer being encoded writes sub_out instead of adding into resid
         Buf resid, normed, operand_bf16, proj, lat, wide, lat_wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;
@@ -767,6 +806,7 @@ static void rope_tables(const RopeCfg& c, uint32_t count, float* cosines, float*
 static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std::string& dir);
 static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string& dir);
 static void load_vugipel_model(uzu_engine* e, const Json& cfg, const std::string& dir);
+static void load_vakesun_model(uzu_engine* e, const Json& cfg, const std::string& dir);
 static void load_language_model_config(uzu_engine* e, const Json& cfg, const std::string& dir);
 
 // Model registry: config.json names its family, either by the reference's type tag or by an "architecture" string.
@@ -780,6 +820,7 @@ static const ModelFamily kModelFamilies[] = {
     {"Punilix", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Punilix"; }, load_parallel_block_model},
     {"Gamanex", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Gamanex"; }, load_gamanex_model},
     {"Vugipel", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Vugipel"; }, load_vugipel_model},
+    {"Vakesun", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Vakesun"; }, load_vakesun_model},
 };
 
 static void load_model(uzu_engine* e, const std::string& dir) {
@@ -974,6 +1015,7 @@ static void alloc_layer_state(uzu_engine* e, const Layer& L, LayerState& S, uint
             break;
         }
         case MixLatentAttention: {   // one row per token: [latent | rotated key part], shared by all heads; no separate values
+            if (L.la.kv_from >= 0) break;   // reads another layer's rows
             S.row_bytes = (size_t)(L.la.rank + L.la.rot_dim) * storage_size(e->store_dt);
             paged(S.k_sparse, S.k_dense, S.keys, (size_t)rows_total * S.row_bytes);
             break;
@@ -1004,6 +1046,12 @@ static void alloc_layer_state(uzu_engine* e, const Layer& L, LayerState& S, uint
         }
         case MixMinGru: {            // f32 [width]
             S.ssm_bytes = (size_t)L.mg.width * 4;
+            fixed(S.ssm_state, S.ssm_bytes);
+            S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
+            break;
+        }
+        case MixMlstm: {             // f32 [heads, dim, vdim + 1] (the last column is the normaliser), then the running maximum f32 [heads]
+            S.ssm_bytes = ((size_t)L.ml.heads * L.ml.dim * (L.ml.vdim + 1) + L.ml.heads) * 4;
             fixed(S.ssm_state, S.ssm_bytes);
             S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
             break;

@@ -1,10 +1,11 @@
-// Parallel-block families (Punilix, Gamanex) and the sequential-sublayer family Vugipel inside the host engine: configuration, weights, scratch and the encoding of one pass.
+// Parallel-block families (Punilix, Gamanex) and the sequential-sublayer families (Vugipel, Vakesun) inside the host engine: configuration, weights, scratch and the encoding of one pass.
 // Included by engine.cu; the pass driver, the state / cache manager, sampling, CUDA-graph decode and the sequence slots are the engine's own.
 //
 //   x = embed[token]                                                      (f32 residual stream)
 //   Punilix layer:  h = group_rms(x);  x <- x + mixer(h) + mlp(h)         (one norm feeds both sublayers)
 //   Gamanex layer:  h1 = rms(x) n1, h2 = rms(x) n2;  x <- x + ls1 sigmoid(G1 h1 + b1) mixer(h1) + ls2 sigmoid(G2 h2 + b2) mlp(h2)
 //   Vugipel layer:  x <- x + mixer(rms(x) (1 + n1));  x <- x + mlp(rms(x) (1 + n2))     (Layer::sequential)
+//   Vakesun layer:  x <- x + m post1(mixer(pre1(x)));  x <- x + m post2(mlp(pre2(x)));  x <- x + m rms(token input(x))    (Layer::sandwich)
 //   logits = cap * tanh(head . group_rms(x) / cap)   |   logit_scale * head . rms(x)
 //
 // Both are described by the same Layer fields (a second norm, sublayer gates and a logit scale are optional parts) and encoded by the same
@@ -183,6 +184,8 @@ static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std:
             append(in, read_floats(pl, p + "mix.dkv", {A.rank + A.rot_dim, W}));
             append(in, read_floats(pl, p + "mix.g", {A.heads * A.vdim, W}));
             A.in = upload_matrix(e, in, A.q_rank + A.rank + A.rot_dim + A.heads * A.vdim, W);
+            A.kv_offset = A.q_rank;
+            A.gate_offset = A.q_rank + A.rank + A.rot_dim;
             A.q_up = upload_matrix(e, read_floats(pl, p + "mix.uq", {A.heads * qd, A.q_rank}).v, A.heads * qd, A.q_rank);
             {   // per head the key up-projection [dim, rank] becomes [rank, dim]: q_abs = (W_uk^h)^T q^h as a linear with weight [out = rank, in = dim]
                 HostTensor uk = read_floats(pl, p + "mix.uk", {A.heads * A.dim, A.rank});
@@ -604,6 +607,232 @@ static void load_vugipel_model(uzu_engine* e, const Json& cfg, const std::string
     e->info.state_bytes_per_token = stb;
 }
 
+// Vakesun: sequential sandwich layers, x <- x + m * post(sublayer(pre(x))) with Dynamic Tanh norms (tanh(alpha x) w + b) before AND after
+// every sublayer and a fixed factor m on every addition; a per-layer token input after the feed-forward (a gelu unit of the residual,
+// gated by a row of a second embedding table, projected, RMS-normed and added); scaled input embedding, readout with the embedding table.
+// Mixers: softmax attention with grouped key / value heads, per-head q / k RMS norms and a half-split rotation with YaRN-blended
+// frequencies ("attention": the window-attention kernels without a window); a matrix memory with exponential gates ("mlstm"); latent
+// attention without positions, with a sliding window, a sink term per head, a sigmoid gate per head and optionally another layer's
+// latent cache ("latent_attention"). Feed-forward: relu^2.
+// config.json: "width", "vocab", "norm": {"eps"}, "residual_mult", "embedding": {"scale"}, "token_side": {"dim"}, "layers": [{"type",
+// "mixer": {...}, "mlp": null | {"kind": "dense", "ff"}}]. Tensors: embed, side.embed, final.norm (+ .b, .alpha), l<i>.norm1 / norm1b /
+// norm2 / norm2b (+ .b, .alpha), l<i>.mix.*, l<i>.mlp.{up,down}, l<i>.side.{gate,proj,norm}.
+static void load_vakesun_model(uzu_engine* e, const Json& cfg, const std::string& dir) {
+    if (e->opts.tp_size > 1) throw std::runtime_error("tensor parallelism is not built for the parallel-block families");
+    e->parallel_block = true;
+    e->store_dt = e->opts.storage_f32 ? UZU_DT_F32 : UZU_DT_BF16;
+    const uint32_t W = e->model_dim = cfg_u32(cfg, "width");
+    const uint32_t V = e->vocab = cfg_u32(cfg, "vocab");
+    e->norm_eps = (float)cfg.at("norm").at("eps").number();
+    e->norm_groups = 1;
+    const float mult = (float)cfg.at("residual_mult").number();
+    if (const Json* em = cfg.get("embedding")) {
+        if (!em->is_null()) e->input_scale = (float)em->at("scale").number();
+    }
+    uint32_t side_dim = 0;
+    if (const Json* ts = cfg.get("token_side")) {
+        if (!ts->is_null()) side_dim = cfg_u32(*ts, "dim");
+    }
+    ParameterLoader pl(dir + "/model.safetensors");
+    auto dyt = [&](const std::string& name) {
+        Norm n;
+        n.present = true;
+        n.kind = 1;
+        n.n = W;
+        n.cfg.epsilon = e->norm_eps;
+        n.scales = upload_f32(e, read_floats(pl, name, {W}).v);
+        n.bias = upload_f32(e, read_floats(pl, name + ".b", {W}).v);
+        n.alpha = read_floats(pl, name + ".alpha", {}).v[0];
+        return n;
+    };
+    const auto& lcs = cfg.at("layers").arr;
+    e->pb_embed = upload_matrix(e, read_floats(pl, "embed", {V, W}).v, V, W);
+    e->pb_head = e->pb_embed;        // the readout multiplies with the embedding table itself (without the input scale)
+    if (side_dim) e->pb_side_embed = upload_matrix(e, read_floats(pl, "side.embed", {V, (uint64_t)lcs.size() * side_dim}).v, V, (uint32_t)lcs.size() * side_dim);
+    e->pb_out_norm = dyt("final.norm");
+    uint64_t wbytes = e->pb_head.bytes, kvb = 0, stb = 0;
+    uint32_t n_cache = 0, n_rec = 0;
+    e->layers.resize(lcs.size());
+    for (size_t i = 0; i < lcs.size(); ++i) {
+        const Json& lc = lcs[i];
+        Layer& L = e->layers[i];
+        const std::string p = "l" + std::to_string(i) + ".";
+        L.sequential = true;
+        L.sandwich = true;
+        L.residual_mult = mult;
+        L.pre_mixer = dyt(p + "norm1");
+        L.post_mixer = dyt(p + "norm1b");
+        const std::string type = lc.at("type").str;
+        const Json& mc = lc.at("mixer");
+        if (type == "attention") {
+            L.kind = MixWindowAttention;
+            L.is_attention = true;
+            WindowAttentionLayer& A = L.wa;
+            A.heads = cfg_u32(mc, "heads");
+            A.kv_heads = cfg_u32(mc, "kv_heads");
+            A.dim = cfg_u32(mc, "dim");
+            A.vdim = cfg_u32(mc, "vdim");
+            A.scale = (float)mc.at("scale").number();
+            if (A.heads == 0 || A.kv_heads == 0 || A.heads % A.kv_heads || A.dim == 0 || A.vdim == 0 || A.dim > 512 || A.vdim > 512)
+                throw std::runtime_error(p + "mix: kv_heads must divide heads, head sizes must be in 1..512");
+            if (const Json* rot = mc.get("rot")) {
+                if (!rot->is_null() && cfg_u32(*rot, "dims")) {
+                    RopeCfg rc;
+                    rc.kind = 3;                 // a table row holds the cos / sin of the pairs, whatever channels a pair is made of
+                    rc.base = (float)rot->at("base").number();
+                    rc.head_dim = cfg_u32(*rot, "dims");
+                    rc.max_sequence_length = 0xFFFFFFFFu;
+                    if (rc.head_dim % 2 || rc.head_dim > A.dim) throw std::runtime_error(p + "mix: rot.dims must be even and at most dim");
+                    const Json* sc = rot->get("scaling");
+                    if (sc && !sc->is_null()) {
+                        rc.yarn = true;
+                        rc.scaling_factor = (float)sc->at("factor").number();
+                        rc.original_context_length = cfg_u32(*sc, "original");
+                        rc.high = (float)sc->at("fast").number();
+                        rc.low = (float)sc->at("slow").number();
+                    }
+                    int idx = -1;
+                    for (size_t r = 0; r < e->ropes.size(); ++r)
+                        if (e->ropes[r] == rc) idx = (int)r;
+                    if (idx < 0) { e->ropes.push_back(rc); idx = (int)e->ropes.size() - 1; }
+                    A.rope_index = idx;
+                    A.rot_halves = true;
+                }
+            }
+            const uint32_t qn = A.heads * A.dim, kn = A.kv_heads * A.dim, vn = A.kv_heads * A.vdim;
+            std::vector<float> in;
+            append(in, read_floats(pl, p + "mix.q", {qn, W}));
+            append(in, read_floats(pl, p + "mix.k", {kn, W}));
+            append(in, read_floats(pl, p + "mix.v", {vn, W}));
+            A.q_offset = 0; A.k_offset = qn; A.v_offset = qn + kn;
+            L.side_in = upload_matrix(e, in, qn + kn + vn, W);
+            A.q_norm = upload_f32(e, read_floats(pl, p + "mix.q.norm", {A.dim}).v);
+            A.k_norm = upload_f32(e, read_floats(pl, p + "mix.k.norm", {A.dim}).v);
+            A.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
+            wbytes += L.side_in.bytes + A.out.bytes;
+            kvb += (uint64_t)(kn + vn) * storage_size(e->store_dt);
+            n_cache++;
+        } else if (type == "mlstm") {
+            L.kind = MixMlstm;
+            L.is_attention = false;
+            MlstmLayer& M = L.ml;
+            M.heads = cfg_u32(mc, "heads");
+            M.dim = cfg_u32(mc, "dim");
+            M.vdim = cfg_u32(mc, "vdim");
+            M.gate_cap = (float)mc.at("gate_cap").number();
+            if (M.heads == 0 || M.dim == 0 || M.dim > 1024 || M.vdim == 0 || M.gate_cap < 0.0f) throw std::runtime_error(p + "mix: heads / vdim must be positive, dim in 1..1024, gate_cap not negative");
+            const uint32_t qn = M.heads * M.dim, vn = M.heads * M.vdim;
+            std::vector<float> in, bias;
+            append(in, read_floats(pl, p + "mix.q", {qn, W}));
+            append(in, read_floats(pl, p + "mix.k", {qn, W}));
+            append(in, read_floats(pl, p + "mix.v", {vn, W}));
+            append(in, read_floats(pl, p + "mix.g", {vn, W}));
+            append(in, read_floats(pl, p + "mix.i", {M.heads, W}));
+            append(in, read_floats(pl, p + "mix.f", {M.heads, W}));
+            M.q_offset = 0; M.k_offset = qn; M.v_offset = 2 * qn; M.gate_offset = 2 * qn + vn; M.i_offset = 2 * qn + 2 * vn; M.f_offset = M.i_offset + M.heads;
+            bias.assign(M.i_offset, 0.0f);
+            append(bias, read_floats(pl, p + "mix.i.b", {M.heads}));
+            append(bias, read_floats(pl, p + "mix.f.b", {M.heads}));
+            M.in = upload_matrix(e, in, M.f_offset + M.heads, W);
+            M.in_bias = upload_f32(e, bias);
+            M.norm_weight = upload_f32(e, read_floats(pl, p + "mix.norm", {vn}).v);
+            M.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, vn}).v, W, vn);
+            wbytes += M.in.bytes + M.out.bytes;
+            stb += 2ull * M.heads * M.dim * (M.vdim + 1) * 4;
+            n_rec++;
+        } else if (type == "latent_attention") {
+            L.kind = MixLatentAttention;
+            L.is_attention = true;
+            LatentAttentionLayer& A = L.la;
+            A.heads = cfg_u32(mc, "heads");
+            A.dim = cfg_u32(mc, "dim");
+            A.vdim = cfg_u32(mc, "vdim");
+            A.rank = cfg_u32(mc, "kv_rank");
+            A.q_rank = cfg_u32(mc, "q_rank");
+            A.scale = (float)mc.at("scale").number();
+            A.gate_per_head = true;
+            if (A.heads == 0 || A.dim == 0 || A.rank == 0 || A.rank > 512 || A.vdim == 0 || A.q_rank == 0) throw std::runtime_error(p + "mix: latent size must be in 1..512, heads / dim / vdim / q_rank non-zero");
+            if (const Json* mk = mc.get("mask")) {
+                if (!mk->is_null()) A.window = cfg_u32(*mk, "size");
+            }
+            if (const Json* kf = mc.get("kv_from")) {
+                if (!kf->is_null()) {
+                    A.kv_from = (int)cfg_u32(mc, "kv_from");
+                    if ((size_t)A.kv_from >= i) throw std::runtime_error(p + "mix: kv_from must name an earlier layer");
+                    const Layer& src = e->layers[A.kv_from];
+                    if (src.kind != MixLatentAttention || src.la.kv_from >= 0 || src.la.rank != A.rank || src.la.rot_dim != 0)
+                        throw std::runtime_error(p + "mix: kv_from must name a latent-attention layer that keeps its own latents of the same size");
+                }
+            }
+            std::vector<float> in;
+            append(in, read_floats(pl, p + "mix.dq", {A.q_rank, W}));
+            uint32_t rows = A.q_rank;
+            if (A.kv_from < 0) {
+                A.kv_offset = rows;
+                append(in, read_floats(pl, p + "mix.dkv", {A.rank, W}));
+                rows += A.rank;
+                A.latent_norm = upload_f32(e, read_floats(pl, p + "mix.dkv.norm", {A.rank}).v);
+                kvb += (uint64_t)A.rank * storage_size(e->store_dt);
+                n_cache++;
+            }
+            A.gate_offset = rows;
+            append(in, read_floats(pl, p + "mix.g", {A.heads, W}));
+            rows += A.heads;
+            A.in = upload_matrix(e, in, rows, W);
+            A.q_up = upload_matrix(e, read_floats(pl, p + "mix.uq", {A.heads * A.dim, A.q_rank}).v, A.heads * A.dim, A.q_rank);
+            {   // per head the key up-projection [dim, rank] becomes [rank, dim] (the absorbed form: the query meets the cached latent itself)
+                HostTensor uk = read_floats(pl, p + "mix.uk", {A.heads * A.dim, A.rank});
+                std::vector<float> t((size_t)A.heads * A.rank * A.dim);
+                for (uint32_t h = 0; h < A.heads; ++h)
+                    for (uint32_t d = 0; d < A.dim; ++d)
+                        for (uint32_t r = 0; r < A.rank; ++r) t[((size_t)h * A.rank + r) * A.dim + d] = uk.v[((size_t)h * A.dim + d) * A.rank + r];
+                A.key_absorb = upload_matrix(e, t, A.rank, A.dim, A.heads);
+            }
+            A.value_up = upload_matrix(e, read_floats(pl, p + "mix.uv", {A.heads * A.vdim, A.rank}).v, A.vdim, A.rank, A.heads);
+            A.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
+            A.q_norm = upload_f32(e, read_floats(pl, p + "mix.dq.norm", {A.q_rank}).v);
+            A.sink = upload_f32(e, read_floats(pl, p + "mix.sink", {A.heads}).v);
+            wbytes += A.in.bytes + A.q_up.bytes + A.key_absorb.bytes + A.value_up.bytes + A.out.bytes;
+        } else {
+            throw std::runtime_error("layer type '" + type + "' is not known to the Vakesun family");
+        }
+        if (side_dim) {
+            TokenSide& T = L.side;
+            T.present = true;
+            T.dim = side_dim;
+            T.column = (uint32_t)i * side_dim;
+            T.gate = upload_matrix(e, read_floats(pl, p + "side.gate", {side_dim, W}).v, side_dim, W);
+            T.proj = upload_matrix(e, read_floats(pl, p + "side.proj", {W, side_dim}).v, W, side_dim);
+            T.norm = upload_f32(e, read_floats(pl, p + "side.norm", {W}).v);
+            wbytes += T.gate.bytes + T.proj.bytes + (uint64_t)side_dim * storage_size(e->store_dt);
+        }
+        GatedMlp& M = L.gmlp;
+        const Json* ml = lc.get("mlp");
+        if (!ml || ml->is_null()) continue;
+        L.pre_mlp = dyt(p + "norm2");
+        L.post_mlp = dyt(p + "norm2b");
+        const std::string kind = ml->at("kind").str;
+        if (kind != "dense") throw std::runtime_error("mlp kind '" + kind + "' is not known to the Vakesun family");
+        M.kind = GatedMlp::Dense;
+        M.unit = GatedMlp::ReluSquared;
+        M.f = cfg_u32(*ml, "ff");
+        if (M.f == 0) throw std::runtime_error(p + "mlp: ff must be positive");
+        M.gate_up = upload_matrix(e, read_floats(pl, p + "mlp.up", {M.f, W}).v, M.f, W);
+        M.down = upload_matrix(e, read_floats(pl, p + "mlp.down", {W, M.f}).v, W, M.f);
+        wbytes += M.gate_up.bytes + M.down.bytes;
+    }
+    pl.assert_all_validated();
+    e->info.model_dim = W;
+    e->info.hidden_dim = 0;
+    e->info.vocab_size = V;
+    e->info.num_layers = (uint32_t)e->layers.size();
+    e->info.num_attention_layers = n_cache;
+    e->info.num_delta_net_layers = n_rec;
+    e->info.weight_bytes_per_token = wbytes;
+    e->info.kv_bytes_per_token_per_ctx = kvb;
+    e->info.state_bytes_per_token = stb;
+}
+
 constexpr uint32_t kPromptChunks = 8;  // most key chunks of a row tile of a sigmoid-attention prompt pass
 constexpr uint32_t kSplitRows = 256;   // query rows x key splits of one latent-attention launch that leaves partial softmax states
 
@@ -612,10 +841,12 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     if (!e->parallel_block) return;
     const uint32_t W = e->model_dim;
     uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1, kmax = e->model_dim;
-    uint32_t proj2 = 1, tickets = 1, prompt_partial = 0;
-    bool second_norm = false;
+    uint32_t proj2 = 1, tickets = 1, prompt_partial = 0, factor_heads = 0;
+    bool second_norm = false, sandwich = false;
     for (const Layer& L : e->layers) {
         second_norm = second_norm || L.pre_mlp.present;
+        sandwich = sandwich || L.sandwich;
+        if (L.side.present) { lat = std::max(lat, L.side.dim); kmax = std::max(kmax, L.side.dim); }
         if (L.kind == MixSigmoidAttention) {
             const SigmoidAttentionLayer& A = L.sa;
             proj = std::max(proj, A.in.rows);
@@ -625,6 +856,12 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             if (e->store_dt == UZU_DT_BF16) prompt_partial = std::max(prompt_partial, A.heads * A.vdim);    // chunked tensor-pipe prompt passes
             tickets = std::max(tickets, A.heads);
             kmax = std::max(kmax, A.heads * A.vdim);
+        } else if (L.kind == MixMlstm) {
+            proj = std::max(proj, L.ml.in.rows);
+            wide = std::max(wide, L.ml.heads * L.ml.vdim);
+            gated = std::max(gated, L.ml.heads * L.ml.vdim);
+            kmax = std::max(kmax, L.ml.heads * L.ml.vdim);
+            factor_heads = std::max(factor_heads, L.ml.heads);
         } else if (L.kind == MixMinGru) {
             proj = std::max(proj, L.mg.in.rows);
             gated = std::max(gated, L.mg.width);
@@ -679,6 +916,8 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     P.resid = dev(R * W * 4);
     P.normed = dev(R * W * 4);
     if (second_norm) P.normed2 = dev(R * W * 4);
+    if (sandwich) P.sub_out = dev(R * W * 4);
+    if (factor_heads) P.token_factors = dev(4 * R * factor_heads * 4);
     P.proj2 = dev(R * proj2 * 4);
     P.pair_weight = dev(R * top * 4);
     P.pair_weight_compact = dev(R * top * 4);
@@ -723,8 +962,9 @@ static void encode_dense(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatr
 // multiplied by scale[c] * sigmoid(logits[row, c] + bias[c]); the logits are columns [offset, offset + width) of a [rows, gate_ld] block.
 static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatrix& w, uint64_t a, uint32_t lda, uint32_t rows,
                                  const SublayerGate* g = nullptr, uint64_t gate_block = 0, uint32_t gate_ld = 0, uint32_t a_op = 0) {
-    uzu_dense_linear_args x = dense_args(e, w, a, rows, e->pb.resid.ptr());
-    x.lda = lda; x.accumulate = 1; x.a_op = a_op;
+    // (a sandwich layer's sublayer leaves its result in a scratch block: it goes through a norm of its own before it is added)
+    uzu_dense_linear_args x = dense_args(e, w, a, rows, e->pb.redirect ? e->pb.sub_out.ptr() : e->pb.resid.ptr());
+    x.lda = lda; x.accumulate = e->pb.redirect ? 0 : 1; x.a_op = a_op;
     if (g && g->present) {
         if (g->bias.b) { x.gate = gate_block + (uint64_t)g->offset * 4; x.gate_ld = gate_ld; x.gate_bias = g->bias.ptr(); }
         if (g->scale.b) x.col_scale = g->scale.ptr();
@@ -816,6 +1056,7 @@ static void encode_side_by_side(uzu_engine* e, uzu_command_buffer* cmd, const La
         pa.v_cosines = vcos; pa.v_sines = vsin; pa.v_pairs = v_pairs; pa.dynamic_position = dyn;
         pa.rows = m; pa.heads = A.heads; pa.kv_heads = A.kv_heads; pa.dim = A.dim; pa.vdim = A.vdim;
         pa.q_stride = pa.k_stride = pa.v_stride = ld; pa.prefix = S.length; pa.cache_dt = e->store_dt; pa.epsilon = e->norm_eps;
+        pa.rot_halves = A.rot_halves ? 1 : 0;
         uzu_window_attention_prepare_encode(cmd, &pa);
         uzu_window_attention_args aa{};
         aa.query = P.query.ptr(); aa.keys = S.keys; aa.values = S.values; aa.out = P.mixed.ptr(); aa.dynamic_position = dyn;
@@ -833,8 +1074,8 @@ static void encode_side_by_side(uzu_engine* e, uzu_command_buffer* cmd, const La
             if (aa.splits < 2 || m > kSplitRows) aa.splits = 1;
         }
         uzu_window_attention_encode(cmd, &aa);
-        uzu_dense_linear_args x = dense_args(e, A.out, P.mixed.ptr(), m, P.resid.ptr());
-        x.lda = A.heads * A.vdim; x.accumulate = 1; x.scale = A.share;
+        uzu_dense_linear_args x = dense_args(e, A.out, P.mixed.ptr(), m, P.redirect ? P.sub_out.ptr() : P.resid.ptr());
+        x.lda = A.heads * A.vdim; x.accumulate = P.redirect ? 0 : 1; x.scale = A.share;
         if (A.out_bias.b) x.bias = A.out_bias.ptr();
         uzu_dense_linear_encode(cmd, &x);
     }
@@ -852,8 +1093,8 @@ static void encode_side_by_side(uzu_engine* e, uzu_command_buffer* cmd, const La
         na.rows = m; na.heads = R.heads; na.dim = R.vdim; na.x_stride = rv; na.gate_stride = ld; na.out_stride = rv; na.normalize = 1;
         na.epsilon = e->norm_eps; na.gate_op = 1;
         uzu_head_norm_gate_encode(cmd, &na);
-        uzu_dense_linear_args x = dense_args(e, R.out, P.gated_mix.ptr(), m, P.resid.ptr());
-        x.lda = rv; x.accumulate = 1; x.scale = R.share;
+        uzu_dense_linear_args x = dense_args(e, R.out, P.gated_mix.ptr(), m, P.redirect ? P.sub_out.ptr() : P.resid.ptr());
+        x.lda = rv; x.accumulate = (P.redirect && !L.has_window_attention()) ? 0 : 1; x.scale = R.share;       // the second of two mixers adds to the first
         uzu_dense_linear_encode(cmd, &x);
     }
 }
@@ -885,19 +1126,20 @@ static void encode_general_delta(uzu_engine* e, uzu_command_buffer* cmd, const L
     encode_into_residual(e, cmd, G.out, P.gated_mix.ptr(), HD, m);
 }
 
-static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& own, const PassCtx& pc) {
     const LatentAttentionLayer& A = L.la;
     auto& P = e->pb;
+    LayerState& S = A.kv_from >= 0 ? e->state[A.kv_from] : own;      // a lender ran earlier in this pass: its rows of the pass are in place
     const uint32_t m = pc.m, ld = A.in.rows, qd = A.dim + A.rot_dim, width = A.rank + A.rot_dim;
     const uint64_t dyn = pc.dynamic ? e->decode_state.ptr() : 0;
-    encode_dense(e, cmd, A.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [query latent | kv latent | rotated key | gate]
+    encode_dense(e, cmd, A.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [query latent | kv latent | rotated key | gate]; a borrower has no kv part
     uzu_group_rms_norm_args qn{};
     qn.input = P.proj.ptr(); qn.scales = A.q_norm.ptr(); qn.output = P.lat.ptr();
     qn.rows = m; qn.n = A.q_rank; qn.groups = 1; qn.in_stride = ld; qn.out_stride = A.q_rank; qn.epsilon = e->norm_eps;
     uzu_group_rms_norm_encode(cmd, &qn);
     encode_dense(e, cmd, A.q_up, P.lat.ptr(), A.q_rank, m, P.wide.ptr());                  // q [m, heads, dim + rot_dim]
     uzu_latent_prepare_args pa{};
-    pa.kv = P.proj.ptr() + (uint64_t)A.q_rank * 4; pa.q = P.wide.ptr(); pa.query = P.query.ptr(); pa.cache = S.keys;
+    pa.kv = A.kv_from < 0 ? P.proj.ptr() + (uint64_t)A.kv_offset * 4 : 0; pa.q = A.rot_dim ? P.wide.ptr() : 0; pa.query = P.query.ptr(); pa.cache = S.keys;
     pa.latent_scales = A.latent_norm.ptr();
     if (A.rope_index >= 0) {
         pa.cosines = e->rope_cos[A.rope_index].ptr(); pa.sines = e->rope_sin[A.rope_index].ptr();
@@ -906,7 +1148,10 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
     pa.dynamic_position = dyn;
     pa.rows = m; pa.heads = A.heads; pa.dim = A.dim; pa.rot_dim = A.rot_dim; pa.rank = A.rank; pa.kv_stride = ld; pa.q_stride = A.heads * qd;
     pa.prefix = S.length; pa.cache_dt = e->store_dt; pa.epsilon = e->norm_eps;
-    uzu_latent_prepare_encode(cmd, &pa);
+    if (pa.kv || pa.q) {
+        if (!pa.q) pa.heads = 0;       // no rotated query part: only the cache row's unit runs
+        uzu_latent_prepare_encode(cmd, &pa);
+    }
     if (A.dim) {   // absorbed key projection, one z per head: query[:, h, 0:rank] = q[:, h, 0:dim] . (W_uk^h as [rank, dim])^T
         uzu_dense_linear_args x = dense_args(e, A.key_absorb, P.wide.ptr(), m, P.query.ptr());
         x.lda = A.heads * qd; x.ldd = A.heads * width; x.batch = A.heads;
@@ -918,9 +1163,12 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
     uzu_latent_attention_args aa{};
     aa.query = P.query.ptr(); aa.cache = S.keys; aa.out = P.mixed.ptr(); aa.dynamic_position = dyn;
     aa.rows = m; aa.heads = A.heads; aa.rank = A.rank; aa.rot_dim = A.rot_dim; aa.prefix = S.length; aa.cache_dt = e->store_dt; aa.scale = A.scale;
+    aa.window = A.window; aa.sinks = A.sink.ptr();
+    if (A.gate_per_head) { aa.head_gate = P.proj.ptr() + (uint64_t)A.gate_offset * 4; aa.head_gate_stride = ld; }
     {   // few query rows (decode, short portions): cut the keys so that about two CTAs per SM run. A captured step sizes the cut for the
-        // largest context its graph serves (the graph is captured again when the context outgrows that).
-        const uint32_t bound = pc.dynamic ? attention_bucket(S.length + m) : S.length + m;
+        // largest context its graph serves (the graph is captured again when the context outgrows that); a window bounds it.
+        uint32_t bound = pc.dynamic ? attention_bucket(S.length + m) : S.length + m;
+        if (A.window) bound = std::min(bound, A.window + 31);
         const uint32_t tiles = (bound + 31) / 32, groups = (A.heads + 7) / 8;
         const uint32_t want = std::max(1u, 2u * (uint32_t)e->ctx->sm_count / std::max(1u, m * groups));
         aa.splits = std::min({tiles, want, kSplitRows / std::max(1u, m), 64u});
@@ -932,10 +1180,47 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
         uzu_dense_linear_args x = dense_args(e, A.value_up, P.mixed.ptr(), m, P.gated_mix.ptr());
         x.lda = A.heads * A.rank; x.ldd = A.heads * A.vdim; x.batch = A.heads;
         x.a_z_stride = A.rank; x.w_z_stride = A.value_up.stride(); x.d_z_stride = A.vdim;
-        x.gate = P.proj.ptr() + (uint64_t)(A.q_rank + width) * 4; x.gate_ld = ld;
+        if (!A.gate_per_head) { x.gate = P.proj.ptr() + (uint64_t)A.gate_offset * 4; x.gate_ld = ld; }     // (a gate per head is applied by the attention kernel)
         uzu_dense_linear_encode(cmd, &x);
     }
     encode_into_residual(e, cmd, A.out, P.gated_mix.ptr(), A.heads * A.vdim, m);
+}
+
+// h [m, W] -> matrix memory with exponential gates: one stacked projection [q | k | v | output gate | input-gate logit | forget-gate logit]
+// with the two gate biases, the gates' scan (running maximum carried in the state), the gated linear recurrence with its normaliser
+// column, then per head: division by max(|n . q|, exp(-m)) + 1e-6, unit RMS, weight, sigmoid gate; the output projection follows.
+static void encode_mlstm(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+    const MlstmLayer& M = L.ml;
+    auto& P = e->pb;
+    const uint32_t m = pc.m, ld = M.in.rows, vn = M.heads * M.vdim;
+    {
+        uzu_dense_linear_args x = dense_args(e, M.in, P.normed.ptr(), m, P.proj.ptr());
+        x.lda = e->model_dim; x.bias = M.in_bias.ptr();
+        uzu_dense_linear_encode(cmd, &x);
+    }
+    const uint64_t block = (uint64_t)MAX_ROWS * M.heads * 4;
+    const uint64_t decay = P.token_factors.ptr(), gain = decay + block, floor = gain + block, nq = floor + block;
+    const uint64_t matrix_floats = (uint64_t)M.heads * M.dim * (M.vdim + 1);
+    uzu_exp_gates_args ga{};
+    ga.i_pre = P.proj.ptr() + (uint64_t)M.i_offset * 4; ga.f_pre = P.proj.ptr() + (uint64_t)M.f_offset * 4;
+    ga.state = S.ssm_state.ptr() + matrix_floats * 4;
+    ga.token_decay = decay; ga.token_gain = gain; ga.floor = floor;
+    ga.rows = m; ga.heads = M.heads; ga.i_stride = ga.f_stride = ld; ga.cap = M.gate_cap;
+    uzu_exp_gates_encode(cmd, &ga);
+    uzu_retention_args ra{};
+    ra.q = P.proj.ptr() + (uint64_t)M.q_offset * 4; ra.k = P.proj.ptr() + (uint64_t)M.k_offset * 4; ra.v = P.proj.ptr() + (uint64_t)M.v_offset * 4;
+    ra.state = S.ssm_state.ptr(); ra.out = P.wide.ptr();
+    ra.rows = m; ra.heads = M.heads; ra.dim = M.dim; ra.vdim = M.vdim; ra.q_stride = ra.k_stride = ra.v_stride = ld; ra.out_stride = vn;
+    ra.key_scale = 1.0f; ra.query_scale = 1.0f / sqrtf((float)M.dim);
+    ra.token_decay = decay; ra.token_gain = gain; ra.norm_out = nq;
+    uzu_retention_encode(cmd, &ra);
+    uzu_head_norm_gate_args na{};
+    na.x = P.wide.ptr(); na.scales = M.norm_weight.ptr(); na.gate = P.proj.ptr() + (uint64_t)M.gate_offset * 4; na.out = P.gated_mix.ptr();
+    na.rows = m; na.heads = M.heads; na.dim = M.vdim; na.x_stride = vn; na.gate_stride = ld; na.out_stride = vn; na.normalize = 1;
+    na.epsilon = e->norm_eps; na.gate_op = 0;
+    na.denom = nq; na.denom_floor = floor; na.denom_epsilon = 1e-6f;
+    uzu_head_norm_gate_encode(cmd, &na);
+    encode_into_residual(e, cmd, M.out, P.gated_mix.ptr(), vn, m);
 }
 
 // h [m, W] -> the feed-forward output is added to the residual stream. Passes of at most 8 rows (decode) form gate and up in one launch
@@ -1021,6 +1306,64 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
     uzu_routed_combine_gated_encode(cmd, &ca);
 }
 
+static void encode_mixer(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+    if (L.kind == MixGeneralDelta) encode_general_delta(e, cmd, L, S, pc);
+    else if (L.kind == MixSigmoidAttention) encode_sigmoid_attention(e, cmd, L, S, pc);
+    else if (L.kind == MixMinGru) encode_min_gru(e, cmd, L, S, pc);
+    else if (L.kind == MixMlstm) encode_mlstm(e, cmd, L, S, pc);
+    else if (L.has_window_attention() || L.has_retention()) encode_side_by_side(e, cmd, L, S, pc);
+    else encode_latent_attention(e, cmd, L, S, pc);
+}
+
+static void set_norm(uzu_norm_add_args& a, const Norm& n, bool next) {
+    if (next) { a.next_kind = n.kind; a.next_weight = n.scales.ptr(); a.next_bias = n.bias.ptr(); a.next_alpha = n.alpha; }
+    else { a.kind = n.kind; a.weight = n.scales.ptr(); a.bias = n.bias.ptr(); a.alpha = n.alpha; }
+}
+
+// A sandwich layer: x <- x + mult * post(sublayer(pre(x))) for the mixer, the feed-forward (if any) and the token input (if any). A
+// sublayer leaves its result in P.sub_out; ONE launch then norms it, adds it into the residual stream and norms the updated stream for
+// whatever reads it next (the feed-forward, or the next layer's mixer: `next`; the pass's last layer leaves no normed copy).
+// `normed_ready`: P.normed already holds this layer's normed input (the previous layer's last launch wrote it).
+static void encode_sandwich_layer(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc, const Norm* next, bool normed_ready) {
+    auto& P = e->pb;
+    const uint32_t m = pc.m, W = e->model_dim;
+    const bool has_mlp = L.gmlp.kind != GatedMlp::None;
+    if (!normed_ready) {
+        uzu_norm_add_args a{};
+        a.input = P.resid.ptr(); a.output = P.normed.ptr(); a.rows = m; a.n = W; a.in_stride = W; a.epsilon = e->norm_eps;
+        set_norm(a, L.pre_mixer, false);
+        uzu_norm_add_encode(cmd, &a);
+    }
+    // residual += mult * norm(sub_out); then the norm of whoever reads the stream next, unless another addition comes first
+    auto add = [&](const Norm& post, const Norm* reader) {
+        uzu_norm_add_args a{};
+        a.input = P.sub_out.ptr(); a.residual = P.resid.ptr(); a.rows = m; a.n = W; a.in_stride = W; a.epsilon = e->norm_eps; a.mult = L.residual_mult;
+        set_norm(a, post, false);
+        if (reader) { a.output = P.normed.ptr(); set_norm(a, *reader, true); }
+        uzu_norm_add_encode(cmd, &a);
+    };
+    P.redirect = true;
+    encode_mixer(e, cmd, L, S, pc);
+    add(L.post_mixer, has_mlp ? &L.pre_mlp : (L.side.present ? nullptr : next));
+    if (has_mlp) {
+        encode_gated_mlp(e, cmd, L, pc, P.normed.ptr());
+        add(L.post_mlp, L.side.present ? nullptr : next);
+    }
+    P.redirect = false;
+    if (L.side.present) {
+        const TokenSide& T = L.side;
+        encode_dense(e, cmd, T.gate, P.resid.ptr(), W, m, P.lat.ptr());                  // the gate reads the residual stream itself
+        uzu_token_gate_args ta{};
+        ta.z = P.lat.ptr(); ta.token_ids = e->token_ids.ptr(); ta.table = e->pb_side_embed.w.ptr(); ta.out = P.lat.ptr();
+        ta.rows = m; ta.n = T.dim; ta.vocab = e->vocab; ta.table_stride = e->pb_side_embed.cols; ta.column = T.column; ta.weights_dt = e->store_dt;
+        uzu_token_gate_encode(cmd, &ta);
+        encode_dense(e, cmd, T.proj, P.lat.ptr(), T.dim, m, P.sub_out.ptr());
+        Norm rms;
+        rms.kind = 0; rms.scales = T.norm;
+        add(rms, next);
+    }
+}
+
 static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx& pc, uint32_t row_begin, uint32_t row_end) {
     const uint32_t m = pc.m, W = e->model_dim;
     auto& P = e->pb;
@@ -1028,22 +1371,26 @@ static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd
         cmd->record_error(UZU_ERROR_UNSUPPORTED, "speculation passes are not built for the parallel-block families");
         return;
     }
-    uzu_embedding_f32_encode(cmd, e->token_ids.ptr(), e->pb_embed.w.ptr(), e->store_dt, P.resid.ptr(), m, e->vocab, W);
+    uzu_embedding_f32_scaled_encode(cmd, e->token_ids.ptr(), e->pb_embed.w.ptr(), e->store_dt, P.resid.ptr(), m, e->vocab, W, e->input_scale);
     const bool dump = P.dump && !pc.dynamic && P.layer_dump.b;
+    bool normed_ready = false;
     for (size_t i = 0; i < e->layers.size(); ++i) {
         Layer& L = e->layers[i];
         LayerState& S = e->state[i];
+        if (L.sandwich) {
+            const Norm* next = (i + 1 < e->layers.size() && e->layers[i + 1].sandwich) ? &e->layers[i + 1].pre_mixer : nullptr;
+            encode_sandwich_layer(e, cmd, L, S, pc, next, normed_ready);
+            normed_ready = next != nullptr;
+            if (dump) uzu_command_buffer_encode_copy(cmd, P.resid.ptr(), P.layer_dump.ptr() + (uint64_t)i * MAX_ROWS * W * 4, (size_t)m * W * 4);
+            continue;
+        }
         uzu_group_rms_norm_args na{};
         na.input = P.resid.ptr(); na.scales = L.pre_mixer.scales.ptr(); na.output = P.normed.ptr();
         na.rows = m; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
         const bool second = !L.sequential && L.pre_mlp.present && L.gmlp.kind != GatedMlp::None;      // the feed-forward norms the same x with its own weights
         if (second) { na.scales2 = L.pre_mlp.scales.ptr(); na.output2 = P.normed2.ptr(); }
         uzu_group_rms_norm_encode(cmd, &na);
-        if (L.kind == MixGeneralDelta) encode_general_delta(e, cmd, L, S, pc);
-        else if (L.kind == MixSigmoidAttention) encode_sigmoid_attention(e, cmd, L, S, pc);
-        else if (L.kind == MixMinGru) encode_min_gru(e, cmd, L, S, pc);
-        else if (L.has_window_attention() || L.has_retention()) encode_side_by_side(e, cmd, L, S, pc);
-        else encode_latent_attention(e, cmd, L, S, pc);
+        encode_mixer(e, cmd, L, S, pc);
         if (L.sequential && L.gmlp.kind != GatedMlp::None) {     // the feed-forward norms the residual the mixer has just added to
             uzu_group_rms_norm_args nb = na;
             nb.scales = L.pre_mlp.scales.ptr(); nb.scales2 = 0; nb.output2 = 0;
@@ -1060,10 +1407,17 @@ static void encode_parallel_block_readout(uzu_engine* e, uzu_command_buffer* cmd
     if (row_end <= row_begin) return;
     const uint32_t rows = row_end - row_begin, W = e->model_dim;
     auto& P = e->pb;
-    uzu_group_rms_norm_args na{};
-    na.input = P.resid.ptr() + (uint64_t)row_begin * W * 4; na.scales = e->pb_final_norm.ptr(); na.output = P.normed_rows.ptr();
-    na.rows = rows; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
-    uzu_group_rms_norm_encode(cmd, &na);
+    if (e->pb_out_norm.present) {
+        uzu_norm_add_args a{};
+        a.input = P.resid.ptr() + (uint64_t)row_begin * W * 4; a.output = P.normed_rows.ptr(); a.rows = rows; a.n = W; a.in_stride = W; a.epsilon = e->norm_eps;
+        set_norm(a, e->pb_out_norm, false);
+        uzu_norm_add_encode(cmd, &a);
+    } else {
+        uzu_group_rms_norm_args na{};
+        na.input = P.resid.ptr() + (uint64_t)row_begin * W * 4; na.scales = e->pb_final_norm.ptr(); na.output = P.normed_rows.ptr();
+        na.rows = rows; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
+        uzu_group_rms_norm_encode(cmd, &na);
+    }
     {
         uzu_dense_linear_args x = dense_args(e, e->pb_head, P.normed_rows.ptr(), rows, P.logits_f32.ptr());
         x.lda = W;

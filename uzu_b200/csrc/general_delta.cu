@@ -170,15 +170,20 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(const uzu_head_norm
     const float* gate = a.gate ? reinterpret_cast<const float*>(a.gate) + (size_t)row * a.gate_stride + (size_t)h * a.dim : nullptr;
     const float* sc = a.scales ? reinterpret_cast<const float*>(a.scales) + (size_t)h * a.dim : nullptr;
     float* out = reinterpret_cast<float*>(a.out) + (size_t)row * a.out_stride + (size_t)h * a.dim;
-    float inv = 1.0f;
+    float inv = 1.0f, pre = 1.0f;
+    if (a.denom) {          // the row is first divided by max(|denom|, floor) + denom_epsilon
+        float d = fabsf(reinterpret_cast<const float*>(a.denom)[(size_t)row * a.heads + h]);
+        if (a.denom_floor) d = fmaxf(d, reinterpret_cast<const float*>(a.denom_floor)[(size_t)row * a.heads + h]);
+        pre = 1.0f / (d + a.denom_epsilon);
+    }
     if (a.normalize) {
         float ss = 0.0f;
-        for (uint32_t i = lane; i < a.dim; i += 32) ss = fmaf(x[i], x[i], ss);
+        for (uint32_t i = lane; i < a.dim; i += 32) { const float y = x[i] * pre; ss = fmaf(y, y, ss); }
         ss = warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)a.dim + a.epsilon);
     }
     for (uint32_t i = lane; i < a.dim; i += 32) {
-        float v = x[i] * inv;
+        float v = x[i] * pre * inv;
         if (sc) v *= sc[i];
         if (gate) v *= a.gate_op == 1 ? gate[i] / (1.0f + expf(-gate[i])) : 1.0f / (1.0f + expf(-gate[i]));
         out[i] = v;

@@ -7,7 +7,9 @@
 //            f32 and used by all heads of the group (warp = head, lane = key for the scores, lane = latent channel for the weighted
 //            sum); running maximum / normaliser / accumulator in f32 registers (online softmax), causal bound = the query's own
 //            position. A pass of few query rows (decode) splits the keys over many CTAs and a second kernel merges the partial
-//            softmax states; a prompt's rows fill the GPU by themselves and write their output directly.
+//            softmax states; a prompt's rows fill the GPU by themselves and write their output directly. Options: a sliding window
+//            (only the last `window` positions are visible), a sink per head (one more term exp(sink) in the denominator, with no
+//            key and no value), a gate per head (the head's sum times sigmoid(gate)).
 // The cache holds bf16 or f32 rows; scores, weights and sums are f32.
 #include "common.cuh"
 
@@ -87,8 +89,12 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
     const uint32_t keys = prefix + t + 1;      // causal: positions 0 .. own
-    const uint32_t tiles = (keys + LA_KEYS - 1) / LA_KEYS, per = (tiles + splits - 1) / splits;
-    const uint32_t j_begin = min(keys, split * per * LA_KEYS), j_end = min(keys, (split + 1) * per * LA_KEYS);
+    const uint32_t lo = (a.window && keys > a.window) ? keys - a.window : 0u;      // first visible key of a sliding window
+    // tiles keep their absolute places (a tile starts at a multiple of LA_KEYS, so the flat copy below stays aligned); the keys of the
+    // first tile that lie before the window are masked
+    const uint32_t tile0 = lo / LA_KEYS;
+    const uint32_t tiles = (keys + LA_KEYS - 1) / LA_KEYS - tile0, per = (tiles + splits - 1) / splits;
+    const uint32_t j_begin = min(keys, (tile0 + split * per) * LA_KEYS), j_end = min(keys, (tile0 + (split + 1) * per) * LA_KEYS);
     const uint32_t head = h0 + warp;
     const bool head_ok = head < a.heads;
     const float* q = reinterpret_cast<const float*>(a.query) + ((size_t)t * a.heads + h0) * width;
@@ -180,9 +186,10 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
             }
             s = d0 * a.scale;
         }
+        if (j0 + lane < lo) s = -INFINITY;
         const float m_new = fmaxf(m, warp_max(s));
-        const float p = lane < n ? expf(s - m_new) : 0.0f;
-        const float corr = expf(m - m_new);
+        const float p = (lane < n && s != -INFINITY) ? expf(s - m_new) : 0.0f;
+        const float corr = m == -INFINITY ? 0.0f : expf(m - m_new);
         l = l * corr + warp_sum(p);
         m = m_new;
 #pragma unroll
@@ -200,7 +207,8 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
     if (!head_ok) return;
     if (splits == 1) {
         float* out = reinterpret_cast<float*>(a.out) + ((size_t)t * a.heads + head) * a.rank;
-        const float inv = 1.0f / l;
+        float inv = 1.0f / (a.sinks ? l + expf(reinterpret_cast<const float*>(a.sinks)[head] - m) : l);
+        if (a.head_gate) inv *= 1.0f / (1.0f + expf(-reinterpret_cast<const float*>(a.head_gate)[(size_t)t * a.head_gate_stride + head]));
 #pragma unroll
         for (int i = 0; i < RV; ++i) {
             const uint32_t c = lane + 32 * i;
@@ -222,7 +230,9 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
 
 // grid (query row x head, blocks of 128 channels): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s, splits taken in order.
 // splits <= 64: warp 0 forms the weights of all splits at once, then every thread sums its channel with the loads of a split batch in flight.
-__global__ void __launch_bounds__(128) latent_combine_kernel(const float* partials, float* out, uint32_t splits, uint32_t rank) {
+// A sink adds exp(sink - M) to the denominator; a head gate multiplies the result by its sigmoid.
+__global__ void __launch_bounds__(128) latent_combine_kernel(const float* partials, float* out, uint32_t splits, uint32_t rank, uint32_t heads,
+                                                             const float* sinks, const float* head_gate, uint32_t head_gate_stride) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float weight[64];
@@ -238,8 +248,12 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const float* partia
         const float w0 = m0 == -INFINITY ? 0.0f : expf(m0 - big), w1 = m1 == -INFINITY ? 0.0f : expf(m1 - big);
         weight[lane] = w0;
         weight[lane + 32] = w1;
-        const float total = warp_sum(w0 * l0) + warp_sum(w1 * l1);
-        if (lane == 0) inv_total = 1.0f / total;
+        float total = warp_sum(w0 * l0) + warp_sum(w1 * l1);
+        const uint32_t row = blockIdx.x / heads, head = blockIdx.x % heads;
+        if (sinks) total += expf(sinks[head] - big);
+        float inv = 1.0f / total;
+        if (head_gate) inv *= 1.0f / (1.0f + expf(-head_gate[(size_t)row * head_gate_stride + head]));
+        if (lane == 0) inv_total = inv;
     }
     __syncthreads();
     const uint32_t c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -268,7 +282,7 @@ static void launch_latent_attention(uzu_command_buffer* cmd, const uzu_latent_at
     launch(cmd, "latent_attention_kernel", latent_attention_kernel<T, RV>, grid, dim3(LA_HEADS * 32), smem, a);
     if (splits > 1) {
         launch(cmd, "latent_combine_kernel", latent_combine_kernel, dim3(a.rows * a.heads, (a.rank + 127) / 128), dim3(128), 0, (const float*)a.partials, (float*)a.out,
-               splits, a.rank);
+               splits, a.rank, a.heads, (const float*)a.sinks, (const float*)a.head_gate, a.head_gate_stride);
     }
 }
 

@@ -1,5 +1,5 @@
-// Glue kernels of the parallel-block family (f32 residual stream): grouped RMS norm, embedding rows into f32, the clamped gated unit,
-// tanh, residual add, logit cap, and the routers (by table or by the largest logits: expert-sorted pair lists + weighted, optionally
+// Glue kernels of the parallel-block family (f32 residual stream): grouped RMS norm, norm (RMS or Dynamic Tanh) with residual add and
+// the next norm, embedding rows into f32, the token-gated gelu unit, the clamped gated unit, tanh, residual add, logit cap, and the routers (by table or by the largest logits: expert-sorted pair lists + weighted, optionally
 // gated combine). Everything is f32 arithmetic.
 #include "common.cuh"
 
@@ -45,8 +45,79 @@ __global__ void __launch_bounds__(256) group_rms_norm_kernel(const uzu_group_rms
     }
 }
 
+// One CTA per row. RMS norm: the row's sum of squares first; Dynamic Tanh is elementwise. With a residual the normed row is added into
+// it (times mult) and the updated row can be normed again for the next sublayer; a second RMS norm takes a second sum over the row.
+__device__ __forceinline__ float norm_add_value(uint32_t kind, float x, float inv, float alpha, const float* w, const float* b, uint32_t i) {
+    float v = kind == 1 ? tanhf(alpha * x) : x * inv;
+    if (w) v *= w[i];
+    if (b) v += b[i];
+    return v;
+}
+
+__global__ void __launch_bounds__(256) norm_add_kernel(const uzu_norm_add_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[32];
+    const uint32_t row = blockIdx.x;
+    const float* in = reinterpret_cast<const float*>(a.input) + (size_t)row * a.in_stride;
+    const float* w = reinterpret_cast<const float*>(a.weight);
+    const float* b = reinterpret_cast<const float*>(a.bias);
+    float inv = 1.0f;
+    if (a.kind == 0) {
+        float ss = 0.0f;
+        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+        ss = block_sum(ss, red);
+        inv = 1.0f / sqrtf(ss / (float)a.n + a.epsilon);
+    }
+    float* out = a.output ? reinterpret_cast<float*>(a.output) + (size_t)row * a.n : nullptr;
+    if (!a.residual) {
+        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) out[i] = norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i);
+        return;
+    }
+    float* res = reinterpret_cast<float*>(a.residual) + (size_t)row * a.n;
+    const float* nw = reinterpret_cast<const float*>(a.next_weight);
+    const float* nb = reinterpret_cast<const float*>(a.next_bias);
+    if (!out || a.next_kind == 1) {
+        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) {
+            const float x = fmaf(a.mult, norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i), res[i]);
+            res[i] = x;
+            if (out) out[i] = norm_add_value(1, x, 1.0f, a.next_alpha, nw, nb, i);
+        }
+        return;
+    }
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) {
+        const float x = fmaf(a.mult, norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i), res[i]);
+        res[i] = x;           // read back below by the thread that wrote it
+        ss = fmaf(x, x, ss);
+    }
+    __syncthreads();          // `red` is free again
+    ss = block_sum(ss, red);
+    const float inv2 = 1.0f / sqrtf(ss / (float)a.n + a.epsilon);
+    for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) out[i] = norm_add_value(0, res[i], inv2, 0.0f, nw, nb, i);
+}
+
 template <typename TW>
-__global__ void embedding_f32_kernel(const uint32_t* tokens, const TW* table, float* out, uint32_t vocab, uint32_t n) {
+__global__ void token_gate_kernel(const uzu_token_gate_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)a.rows * a.n) return;
+    const uint32_t r = (uint32_t)(idx / a.n), i = (uint32_t)(idx % a.n);
+    const uint32_t tok = reinterpret_cast<const uint32_t*>(a.token_ids)[r];
+    float e = 0.0f;
+    if (tok < a.vocab) {
+        const TW* t = reinterpret_cast<const TW*>(a.table) + (size_t)tok * a.table_stride + a.column + i;
+        if constexpr (sizeof(TW) == 2) e = __bfloat162float(*t);
+        else e = *t;
+    }
+    const float z = reinterpret_cast<const float*>(a.z)[idx];
+    const float g = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    reinterpret_cast<float*>(a.out)[idx] = g * e;
+}
+
+template <typename TW>
+__global__ void embedding_f32_kernel(const uint32_t* tokens, const TW* table, float* out, uint32_t vocab, uint32_t n, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t row = blockIdx.y;
@@ -58,7 +129,7 @@ __global__ void embedding_f32_kernel(const uint32_t* tokens, const TW* table, fl
         if constexpr (sizeof(TW) == 2) v = __bfloat162float(table[(size_t)tok * n + i]);
         else v = table[(size_t)tok * n + i];
     }
-    out[(size_t)row * n + i] = v;
+    out[(size_t)row * n + i] = v * scale;
 }
 
 __global__ void clamped_glu_kernel(const float* gate_up, float* out, uint32_t rows, uint32_t f, float limit, float alpha) {
@@ -336,14 +407,43 @@ void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_rms_norm
     launch(cmd, "group_rms_norm_kernel", group_rms_norm_kernel, dim3(b.rows, b.groups), dim3(256), 0, b);
 }
 
-void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output, uint32_t rows,
-                              uint32_t vocab, uint32_t n) {
+void uzu_embedding_f32_scaled_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output, uint32_t rows,
+                                     uint32_t vocab, uint32_t n, float scale) {
     if (!encodable(cmd, "embedding_f32") || rows == 0 || n == 0) return;
     dim3 grid(blocks256(n), rows);
     if (weights_dt == UZU_DT_BF16)
-        launch(cmd, "embedding_f32_kernel", embedding_f32_kernel<__nv_bfloat16>, grid, dim3(256), 0, (const uint32_t*)token_ids, (const __nv_bfloat16*)table, (float*)output, vocab, n);
+        launch(cmd, "embedding_f32_kernel", embedding_f32_kernel<__nv_bfloat16>, grid, dim3(256), 0, (const uint32_t*)token_ids, (const __nv_bfloat16*)table, (float*)output, vocab, n, scale);
     else
-        launch(cmd, "embedding_f32_kernel", embedding_f32_kernel<float>, grid, dim3(256), 0, (const uint32_t*)token_ids, (const float*)table, (float*)output, vocab, n);
+        launch(cmd, "embedding_f32_kernel", embedding_f32_kernel<float>, grid, dim3(256), 0, (const uint32_t*)token_ids, (const float*)table, (float*)output, vocab, n, scale);
+}
+
+void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output, uint32_t rows,
+                              uint32_t vocab, uint32_t n) {
+    uzu_embedding_f32_scaled_encode(cmd, token_ids, table, weights_dt, output, rows, vocab, n, 1.0f);
+}
+
+void uzu_norm_add_encode(uzu_command_buffer* cmd, const uzu_norm_add_args* a) {
+    if (!encodable(cmd, "norm_add")) return;
+    if (!a->input || (!a->residual && !a->output) || a->kind > 1 || a->next_kind > 1) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "norm_add: null operand or unknown norm kind");
+        return;
+    }
+    if (a->rows == 0 || a->n == 0) return;
+    uzu_norm_add_args b = *a;
+    if (!b.in_stride) b.in_stride = b.n;
+    launch(cmd, "norm_add_kernel", norm_add_kernel, dim3(b.rows), dim3(256), 0, b);
+}
+
+void uzu_token_gate_encode(uzu_command_buffer* cmd, const uzu_token_gate_args* a) {
+    if (!encodable(cmd, "token_gate")) return;
+    if (!a->z || !a->token_ids || !a->table || !a->out || (a->weights_dt != UZU_DT_BF16 && a->weights_dt != UZU_DT_F32) || a->column + a->n > a->table_stride) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "token_gate: null operand, bad table type, or columns outside the table");
+        return;
+    }
+    if (a->rows == 0 || a->n == 0) return;
+    const dim3 grid(blocks256((size_t)a->rows * a->n));
+    if (a->weights_dt == UZU_DT_BF16) launch(cmd, "token_gate_kernel", token_gate_kernel<__nv_bfloat16>, grid, dim3(256), 0, *a);
+    else launch(cmd, "token_gate_kernel", token_gate_kernel<float>, grid, dim3(256), 0, *a);
 }
 
 void uzu_clamped_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f, float limit, float alpha) {

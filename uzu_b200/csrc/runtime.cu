@@ -96,6 +96,7 @@ size_t uzu_abi_struct_size(const char* name) {
     UZU_SZ(uzu_dense_linear_args) UZU_SZ(uzu_group_rms_norm_args) UZU_SZ(uzu_table_route_args) UZU_SZ(uzu_general_delta_args) UZU_SZ(uzu_head_norm_gate_args)
     UZU_SZ(uzu_latent_prepare_args) UZU_SZ(uzu_latent_attention_args) UZU_SZ(uzu_topk_route_args) UZU_SZ(uzu_routed_combine_args)
     UZU_SZ(uzu_sigmoid_attention_prepare_args) UZU_SZ(uzu_sigmoid_attention_args)
+    UZU_SZ(uzu_exp_gates_args) UZU_SZ(uzu_norm_add_args) UZU_SZ(uzu_token_gate_args)
     UZU_SZ(uzu_min_gru_args) UZU_SZ(uzu_retention_args) UZU_SZ(uzu_window_attention_prepare_args) UZU_SZ(uzu_window_attention_args)
 #undef UZU_SZ
     return 0;

@@ -1,7 +1,8 @@
 // Windowed softmax attention with kept first tokens, rotated keys AND rotated values.
 //   visibility:  key j is seen from position p when j <= p and (p - j < window or j < keep_first); kept tokens keep their true positions
 //   score:       s = scale * temp[h] * q . k, then softcap * tanh(s / softcap); ordinary softmax over the visible keys
-//   rotation:    q and k turn by their position over the first 2 * rot_pairs channels (pairs (2i, 2i+1)); the value of position j turns
+//   rotation:    q and k turn by their position over the first 2 * rot_pairs channels (pairs (2i, 2i+1), or (i, i + rot_pairs) with
+//                rot_halves); the value of position j turns
 //                by j over 2 * v_pairs channels with its own frequencies and is cached so; a head's weighted sum at position p is turned
 //                back by -p. (The sum then holds every value turned by j - p, a relative position, without a second pass over the cache.)
 //   prepare:     per token and head the RMS norm over the head's channels (one weight row shared by the heads), the rotation, the f32
@@ -60,6 +61,21 @@ __device__ __forceinline__ void wa_rotate_row(const float* src, float inv, const
     }
 }
 
+// the same with the pairs laid out as two halves: channel i turns with channel i + pairs (i < pairs), channels from 2 * pairs on are copied
+template <typename TO>
+__device__ __forceinline__ void wa_rotate_row_halves(const float* src, float inv, const float* scales, TO* out, uint32_t n, uint32_t pairs,
+                                                     const float* cosines, const float* sines, uint32_t lane) {
+    for (uint32_t i = lane; i < pairs; i += 32) {
+        const uint32_t c0 = i, c1 = i + pairs;
+        const float x0 = src[c0] * inv * (scales ? scales[c0] : 1.0f);
+        const float x1 = src[c1] * inv * (scales ? scales[c1] : 1.0f);
+        const float c = cosines[i], s = sines[i];
+        wa_store<TO>(out + c0, x0 * c - x1 * s);
+        wa_store<TO>(out + c1, x1 * c + x0 * s);
+    }
+    for (uint32_t i = 2 * pairs + lane; i < n; i += 32) wa_store<TO>(out + i, src[i] * inv * (scales ? scales[i] : 1.0f));
+}
+
 __device__ __forceinline__ float wa_head_inv_rms(const float* src, uint32_t n, float eps, uint32_t lane) {
     float ss = 0.0f;
     for (uint32_t i = lane; i < n; i += 32) ss = fmaf(src[i], src[i], ss);
@@ -100,13 +116,17 @@ __global__ void __launch_bounds__(128) window_attention_prepare_kernel(const uzu
         const float* src = reinterpret_cast<const float*>(a.q) + (size_t)t * a.q_stride + (size_t)unit * a.dim;
         const float* sc = reinterpret_cast<const float*>(a.q_scales);
         const float inv = sc ? wa_head_inv_rms(src, a.dim, a.epsilon, lane) : 1.0f;
-        wa_rotate_row<float>(src, inv, sc, reinterpret_cast<float*>(a.query) + ((size_t)t * a.heads + unit) * a.dim, a.dim, a.rot_pairs, cs, sn, lane);
+        float* dst = reinterpret_cast<float*>(a.query) + ((size_t)t * a.heads + unit) * a.dim;
+        if (a.rot_halves) wa_rotate_row_halves<float>(src, inv, sc, dst, a.dim, a.rot_pairs, cs, sn, lane);
+        else wa_rotate_row<float>(src, inv, sc, dst, a.dim, a.rot_pairs, cs, sn, lane);
     } else if (unit < a.heads + a.kv_heads) {
         const uint32_t g = unit - a.heads;
         const float* src = reinterpret_cast<const float*>(a.k) + (size_t)t * a.k_stride + (size_t)g * a.dim;
         const float* sc = reinterpret_cast<const float*>(a.k_scales);
         const float inv = sc ? wa_head_inv_rms(src, a.dim, a.epsilon, lane) : 1.0f;
-        wa_rotate_row<T>(src, inv, sc, reinterpret_cast<T*>(a.keys) + ((size_t)pos * a.kv_heads + g) * a.dim, a.dim, a.rot_pairs, cs, sn, lane);
+        T* dst = reinterpret_cast<T*>(a.keys) + ((size_t)pos * a.kv_heads + g) * a.dim;
+        if (a.rot_halves) wa_rotate_row_halves<T>(src, inv, sc, dst, a.dim, a.rot_pairs, cs, sn, lane);
+        else wa_rotate_row<T>(src, inv, sc, dst, a.dim, a.rot_pairs, cs, sn, lane);
     } else {
         const uint32_t g = unit - a.heads - a.kv_heads;
         const float* src = reinterpret_cast<const float*>(a.v) + (size_t)t * a.v_stride + (size_t)g * a.vdim;

@@ -422,7 +422,7 @@ def write_punilix_model(config: dict, path, seed: int = 0, tensors: dict | None 
     out = {}
     for name, v in tensors.items():
         v = np.asarray(v)
-        out[name] = np.ascontiguousarray(v, np.int32) if np.issubdtype(v.dtype, np.integer) else st.as_bf16(f32_to_bf16_bits(v.astype(np.float32)))
+        out[name] = np.ascontiguousarray(v, np.int32) if np.issubdtype(v.dtype, np.integer) else st.as_bf16(f32_to_bf16_bits(v.astype(np.float32)).reshape(v.shape))
     st.save(path / "model.safetensors", out)
     return path
 
@@ -627,3 +627,120 @@ def vugipel_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=8, top=2,
         layers.append(vugipel_parallel_layer(heads, max(heads // 4, 1), 128, 128, window, keep_first, max(heads // 2, 1), 128, 128,
                                              vugipel_moe_mlp(ff // top, experts, top), softcap=30.0, left_scale=0.8, right_scale=1.1))
     return vugipel_config(width, vocab, layers, eps=1e-5)
+
+
+# ---- Vakesun: sandwich layers with Dynamic Tanh norms; attention, matrix memory (mLSTM) and windowed latent attention mixers ----------------
+
+def vakesun_attention_layer(heads: int, kv_heads: int, dim: int, vdim: int, mlp: dict | None, scale: float | None = None, rot_dims: int | None = None,
+                            rot_base: float = 10000.0, scaling: dict | None = None) -> dict:
+    rot_dims = dim if rot_dims is None else rot_dims
+    rot = {"base": rot_base, "dims": rot_dims}
+    if scaling:
+        rot["scaling"] = scaling
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5 if scale is None else scale}
+    if rot_dims:
+        mixer["rot"] = rot
+    return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+
+def vakesun_mlstm_layer(heads: int, dim: int, vdim: int, mlp: dict | None, gate_cap: float = 15.0) -> dict:
+    return {"type": "mlstm", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": gate_cap}, "mlp": mlp}
+
+
+def vakesun_latent_layer(heads: int, dim: int, vdim: int, kv_rank: int, q_rank: int, window: int, mlp: dict | None, scale: float | None = None,
+                         kv_from: int | None = None) -> dict:
+    mixer = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "mask": {"size": window},
+             "scale": dim ** -0.5 if scale is None else scale}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+
+
+def vakesun_dense_mlp(ff: int) -> dict:
+    return {"kind": "dense", "ff": ff}
+
+
+def vakesun_config(width: int, vocab: int, layers: list, eps: float = 1e-6, residual_mult: float = 0.5, embedding_scale: float = 1.0,
+                   side_dim: int = 8) -> dict:
+    return {"architecture": "Vakesun", "width": width, "vocab": vocab, "norm": {"eps": eps}, "residual_mult": residual_mult,
+            "embedding": {"scale": embedding_scale}, "token_side": {"dim": side_dim}, "layers": layers}
+
+
+def vakesun_tensors(config: dict, seed: int = 0) -> dict:
+    """Seeded random tensors of a Vakesun config: f32 values that bf16 holds exactly."""
+    rng = np.random.default_rng(seed)
+    W, V = config["width"], config["vocab"]
+    sd = config["token_side"]["dim"] if config.get("token_side") else 0
+    nl = len(config["layers"])
+
+    def bf(x):
+        return st_bits_to_f32(f32_to_bf16_bits(np.asarray(x, np.float32)))
+
+    def mat(rows, cols, gain=1.0):
+        return bf(rng.standard_normal((rows, cols), dtype=np.float32) * (gain / np.sqrt(cols)))
+
+    def vec(n, mean=0.0, spread=0.1):
+        return bf(mean + spread * rng.standard_normal(n, dtype=np.float32))
+
+    t = {"embed": mat(V, W, np.sqrt(W))}
+
+    def dyt(name, alpha):
+        t[name], t[name + ".b"] = vec(W, 1.0, 0.2), vec(W, 0.0, 0.1)
+        t[name + ".alpha"] = bf(np.float32(alpha * (1.0 + 0.2 * rng.standard_normal()))).reshape(())      # a scalar
+
+    dyt("final.norm", 0.6)
+    if sd:
+        t["side.embed"] = mat(V, nl * sd, np.sqrt(nl * sd))
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        m = L["mixer"]
+        dyt(p + "norm1", 0.7)
+        dyt(p + "norm1b", 1.0)
+        if L["type"] == "attention":
+            H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(H * D, W, 1.5), mat(G * D, W, 1.5), mat(G * Dv, W)
+            t[p + "mix.q.norm"], t[p + "mix.k.norm"] = vec(D, 1.0, 0.2), vec(D, 1.0, 0.2)
+            t[p + "mix.o"] = mat(W, H * Dv)
+        elif L["type"] == "mlstm":
+            H, D, Dv = m["heads"], m["dim"], m["vdim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = mat(H * D, W, 1.5), mat(H * D, W, 1.5), mat(H * Dv, W), mat(H * Dv, W, 1.5)
+            t[p + "mix.i"], t[p + "mix.i.b"] = mat(H, W, 2.0), vec(H, 0.0, 1.0)
+            t[p + "mix.f"], t[p + "mix.f.b"] = mat(H, W, 2.0), vec(H, 3.0, 1.0)
+            t[p + "mix.norm"], t[p + "mix.o"] = vec(H * Dv, 1.0, 0.2), mat(W, H * Dv)
+        else:
+            H, D, Dv, R, Q = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"], t[p + "mix.dq.norm"], t[p + "mix.uq"] = mat(Q, W), vec(Q, 1.0, 0.2), mat(H * D, Q, 1.5)
+            if m.get("kv_from") is None:
+                t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = mat(R, W), vec(R, 1.0, 0.2)
+            t[p + "mix.uk"], t[p + "mix.uv"] = mat(H * D, R, 1.5), mat(H * Dv, R)
+            t[p + "mix.sink"], t[p + "mix.g"] = vec(H, 0.5, 1.0), mat(H, W, 2.0)
+            t[p + "mix.o"] = mat(W, H * Dv)
+        if L.get("mlp") is not None:
+            f = L["mlp"]["ff"]
+            dyt(p + "norm2", 0.7)
+            dyt(p + "norm2b", 1.0)
+            t[p + "mlp.up"], t[p + "mlp.down"] = mat(f, W, 1.5), mat(W, f)
+        if sd:
+            t[p + "side.gate"], t[p + "side.proj"], t[p + "side.norm"] = mat(sd, W, 1.5), mat(W, sd), vec(W, 1.0, 0.2)
+    return t
+
+
+def write_vakesun_model(config: dict, path, seed: int = 0, tensors: dict | None = None) -> Path:
+    """config.json + model.safetensors (bf16). `tensors` overrides the seeded random ones (values are rounded to bf16)."""
+    return write_punilix_model(config, path, seed, tensors if tensors is not None else vakesun_tensors(config, seed))
+
+
+def vakesun_preset(width=2048, vocab=32768, blocks=3, ff=None, window=512, side_dim=256) -> dict:
+    """A layer stack of realistic sizes for benchmarks: per block a windowed latent-attention layer, a full attention layer, a matrix-memory
+    layer without feed-forward and a second latent-attention layer that reads the first one's latents."""
+    ff = ff or 4 * width
+    heads = max(width // 128, 1)
+    yarn = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    layers = []
+    for b in range(blocks):
+        first = len(layers)
+        layers.append(vakesun_latent_layer(heads, 128, 128, 512, min(1536, width), window, vakesun_dense_mlp(ff)))
+        layers.append(vakesun_attention_layer(heads, max(heads // 4, 1), 128, 128, vakesun_dense_mlp(ff), rot_dims=64, rot_base=1e6, scaling=yarn))
+        layers.append(vakesun_mlstm_layer(max(heads // 2, 1), 128, 128, None))
+        layers.append(vakesun_latent_layer(heads, 128, 128, 512, min(1536, width), window, vakesun_dense_mlp(ff), kv_from=first))
+    return vakesun_config(width, vocab, layers, eps=1e-6, residual_mult=0.3, embedding_scale=1.0, side_dim=side_dim)
