@@ -228,3 +228,85 @@ def forward(cfg, W, tokens, state=None):
     state["pos"] += T
     logits = dyt(x, W, "final.norm") @ W["embed"].to(F64).T
     return logits, torch.stack(per_layer), state
+
+
+# ---- small configurations and random weights for the tests -----------------------------------------------------------------------------
+def attention_layer(heads, kv_heads, dim, vdim, mlp_ff=None, rot_dims=None, base=10000.0, scaling=None, scale=None):
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5 if scale is None else scale}
+    rot_dims = dim if rot_dims is None else rot_dims
+    if rot_dims:
+        mixer["rot"] = {"base": base, "dims": rot_dims}
+        if scaling:
+            mixer["rot"]["scaling"] = scaling
+    return {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": mlp_ff} if mlp_ff else None}
+
+
+def mlstm_layer(heads, dim, vdim, mlp_ff=None, gate_cap=15.0):
+    return {"type": "mlstm", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "gate_cap": gate_cap}, "mlp": {"kind": "dense", "ff": mlp_ff} if mlp_ff else None}
+
+
+def latent_layer(heads, dim, vdim, kv_rank, q_rank, window, mlp_ff=None, scale=None, kv_from=None):
+    mixer = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "mask": {"size": window},
+             "scale": dim ** -0.5 if scale is None else scale}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": mlp_ff} if mlp_ff else None}
+
+
+def make_config(width, vocab, layers, eps=1e-6, residual_mult=0.5, embedding_scale=1.0, side_dim=8):
+    return {"architecture": "Vakesun", "width": width, "vocab": vocab, "norm": {"eps": eps}, "residual_mult": residual_mult,
+            "embedding": {"scale": embedding_scale}, "token_side": {"dim": side_dim}, "layers": layers}
+
+
+def random_weights(cfg, seed=0):
+    """bf16-exact random tensors (torch.bfloat16) with spreads that keep every mechanism active: gates away from saturation, sinks of the
+    size of the scores, norm scalars near 1."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = cfg["width"], cfg["vocab"]
+    sd = cfg["token_side"]["dim"] if cfg.get("token_side") else 0
+    w = {}
+
+    def mat(rows, cols, gain=1.0):
+        return (torch.randn(rows, cols, generator=g) * gain / math.sqrt(cols)).to(torch.bfloat16)
+
+    def vec(n, mean=0.0, spread=0.1):
+        return (mean + spread * torch.randn(n, generator=g)).to(torch.bfloat16)
+
+    def norm(name, alpha):
+        w[name], w[name + ".b"] = vec(W, 1.0, 0.2), vec(W, 0.0, 0.1)
+        w[name + ".alpha"] = torch.tensor(alpha * (1.0 + 0.2 * float(torch.randn((), generator=g)))).to(torch.bfloat16)
+
+    w["embed"] = mat(V, W, math.sqrt(W))
+    if sd:
+        w["side.embed"] = mat(V, len(cfg["layers"]) * sd, math.sqrt(len(cfg["layers"]) * sd))
+    norm("final.norm", 0.6)
+    for i, lc in enumerate(cfg["layers"]):
+        p, m = "l%d." % i, lc["mixer"]
+        norm(p + "norm1", 0.7)
+        norm(p + "norm1b", 1.0)
+        if lc["type"] == "attention":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"] = mat(H * d, W, 1.5), mat(G * d, W, 1.5), mat(G * dv, W)
+            w[p + "mix.q.norm"], w[p + "mix.k.norm"] = vec(d, 1.0, 0.2), vec(d, 1.0, 0.2)
+            w[p + "mix.o"] = mat(W, H * dv)
+        elif lc["type"] == "mlstm":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            w[p + "mix.q"], w[p + "mix.k"], w[p + "mix.v"], w[p + "mix.g"] = mat(H * d, W, 1.5), mat(H * d, W, 1.5), mat(H * dv, W), mat(H * dv, W, 1.5)
+            w[p + "mix.i"], w[p + "mix.i.b"] = mat(H, W, 2.0), vec(H, 0.0, 1.0)
+            w[p + "mix.f"], w[p + "mix.f.b"] = mat(H, W, 2.0), vec(H, 3.0, 1.0)
+            w[p + "mix.norm"], w[p + "mix.o"] = vec(H * dv, 1.0, 0.2), mat(W, H * dv)
+        else:
+            H, d, dv, R, Q = m["heads"], m["dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            w[p + "mix.dq"], w[p + "mix.dq.norm"], w[p + "mix.uq"] = mat(Q, W), vec(Q, 1.0, 0.2), mat(H * d, Q, 1.5)
+            if m.get("kv_from") is None:
+                w[p + "mix.dkv"], w[p + "mix.dkv.norm"] = mat(R, W), vec(R, 1.0, 0.2)
+            w[p + "mix.uk"], w[p + "mix.uv"] = mat(H * d, R, 1.5), mat(H * dv, R)
+            w[p + "mix.sink"], w[p + "mix.g"] = vec(H, 0.5, 1.0), mat(H, W, 2.0)
+            w[p + "mix.o"] = mat(W, H * dv)
+        if lc.get("mlp"):
+            norm(p + "norm2", 0.7)
+            norm(p + "norm2b", 1.0)
+            w[p + "mlp.up"], w[p + "mlp.down"] = mat(lc["mlp"]["ff"], W, 1.5), mat(W, lc["mlp"]["ff"])
+        if sd:
+            w[p + "side.gate"], w[p + "side.proj"], w[p + "side.norm"] = mat(sd, W, 1.5), mat(W, sd), vec(W, 1.0, 0.2)
+    return w
