@@ -717,7 +717,9 @@ def family_models(size: str, family: str = "punilix"):
     block of the same width, feed-forward size, head count and layer count; random weights. Punilix stands beside the 4-bit hybrid
     (gated attention + DeltaNet); Gamanex (attention layers that keep or borrow their cache, dense feed-forwards) beside Punilix; Vugipel
     (minGRU layers with one expert, window attention + retention layers with 2 of 8 routed experts) beside Punilix with a dense
-    feed-forward in its recurrent layers and 2 of 8 table-routed experts in its attention layers."""
+    feed-forward in its recurrent layers and 2 of 8 table-routed experts in its attention layers; Vakesun (windowed latent attention that
+    keeps or borrows its latents, full attention, matrix memory; relu^2 feed-forwards, a per-layer token input) beside Punilix with the
+    same number of layers (at least four)."""
     from uzu_b200 import synth
     width, ff, blocks, vocab = FAMILY_SIZES[size]
     base = Path(os.environ.get("UZU_MODEL_CACHE", "/dev/shm/uzu_b200_models"))
@@ -732,6 +734,16 @@ def family_models(size: str, family: str = "punilix"):
             synth.write_gamanex_model(synth.gamanex_preset(width=width, vocab=vocab, blocks=blocks, ff=ff), gdir, seed=0)
             (gdir / ".done").write_text("ok")
         return [("gamanex", gdir, 2.0), ("closest_existing", pdir, 2.0)]
+    if family == "vakesun":     # beside Punilix (latent attention + a matrix-state recurrence, dense feed-forwards) with the same number of layers
+        layers = max(4, 2 * blocks)
+        vdir, mdir = base / f"vakesun-{size}", base / f"punilix-{size}-{layers}"
+        if not (vdir / ".done").exists():
+            synth.write_vakesun_model(synth.vakesun_preset(width=width, vocab=vocab, layers=layers, ff=ff, window=512, side_dim=256), vdir, seed=0)
+            (vdir / ".done").write_text("ok")
+        if not (mdir / ".done").exists():
+            synth.write_punilix_model(synth.punilix_preset(width=width, vocab=vocab, blocks=layers // 2, ff=ff), mdir, seed=0)
+            (mdir / ".done").write_text("ok")
+        return [("vakesun", vdir, 2.0), ("closest_existing", mdir, 2.0)]
     if family == "vugipel":     # beside Punilix with routed experts of the same count and active size in the attention layers
         vdir, mdir = base / f"vugipel-{size}", base / f"punilix-moe-{size}"
         if not (vdir / ".done").exists():
@@ -770,7 +782,7 @@ def family_compare(args):
     with B.Context(0) as ctx:
         for size in sizes:
             models = family_models(size, args.family)
-            line = {"family_compare": size, "family": args.family, "closest_existing": {"gamanex": "punilix (bf16)", "vugipel": "punilix with 2 of 8 table-routed experts (bf16)"}.get(args.family, "gated attention + DeltaNet hybrid (int4)"), "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
+            line = {"family_compare": size, "family": args.family, "closest_existing": {"gamanex": "punilix (bf16)", "vugipel": "punilix with 2 of 8 table-routed experts (bf16)", "vakesun": "punilix with the same number of layers (bf16)"}.get(args.family, "gated attention + DeltaNet hybrid (int4)"), "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
                                                                                                          "tensor_tflops": tens, "tensor_source": tens_src}}
             for name, d, bytes_per_weight in models:
                 with B.Engine(ctx, d, max_context_length=prompt_len + steps + 64, use_cuda_graph=not args.no_graph) as eng:
@@ -818,7 +830,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="decode this many independent sequences together (<= 16), one weight pass per step")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size: shard ONE model over this many ranks (= --gpus) instead of replicas")
-    ap.add_argument("--family", choices=["punilix", "gamanex", "vugipel"], default=None,
+    ap.add_argument("--family", choices=["punilix", "gamanex", "vugipel", "vakesun"], default=None,
                     help="instead of the headline workload: prefill / decode throughput of this model family beside the closest existing one at equal layer sizes (1 GPU)")
     ap.add_argument("--family-sizes", default="", help="comma list of " + ", ".join(sorted(FAMILY_SIZES)) + " (default 1k,2k)")
     args = ap.parse_args()

@@ -486,6 +486,16 @@ typedef struct uzu_dense_linear_args {
     uint64_t col_scale;            /* optional f32 [n]: the product is multiplied by col_scale[col] (a per-channel layer scale) */
     uint64_t row_scale;            /* optional f32 [compact rows]: the product of compact row p is multiplied by row_scale[p] before any
                                       epilogue (paired unit included): a router weight applied to an expert's input, A . W being linear in A */
+    /* Sandwich epilogue (post_weight != 0; batch = 1, no accumulate): the finished product y of an element goes through a Dynamic Tanh
+     * norm of its own and is added into the residual stream D points to, D[row, col] += post_mult * (tanh(post_alpha * y) * post_weight[col]
+     * + post_bias[col]); with next_out the updated element is normed for the next reader, next_out[row, col] = tanh(next_alpha * D[row, col])
+     * * next_weight[col] + next_bias[col] (f32 [rows, ldd]). Both norms are elementwise, so no second pass over the row is needed.
+     * Not on the tcgen05 form (products of >= 128 rows take the other kernels when it is set). */
+    uint64_t post_weight, post_bias, next_weight, next_bias, next_out;
+    float post_alpha, post_mult, next_alpha;
+    uint32_t token_gate_dt;        /* token-gate epilogue (token_table != 0): D = gelu_tanh(y) * token_table[token_ids[row], token_column + col], */
+    uint64_t token_ids, token_table;   /* token_table of type token_gate_dt [vocab, token_table_stride], token_ids u32 [rows] (ids >= token_vocab read 0) */
+    uint32_t token_table_stride, token_column, token_vocab, reserved2;
 } uzu_dense_linear_args;
 UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
 /* 0, or the code of the first bounded barrier wait that ran out inside a tensor-memory dense product (the kernel gives up and returns) */
@@ -650,6 +660,10 @@ typedef struct uzu_latent_prepare_args {
     uint32_t rows, heads, dim, rot_dim, rank, rot_pairs, kv_stride, q_stride, prefix, cache_dt;
     float epsilon;
     uint32_t reserved;
+    /* optional, in the same launch: the RMS norm of the query latent, q_latent_out[t, 0:q_rank] = rms(q_latent[t, 0:q_rank]) * q_latent_scales
+     * (f32, input rows q_latent_stride apart, output rows dense) */
+    uint64_t q_latent, q_latent_scales, q_latent_out;
+    uint32_t q_rank, q_latent_stride;
 } uzu_latent_prepare_args;
 UZU_API void uzu_latent_prepare_encode(uzu_command_buffer* cmd, const uzu_latent_prepare_args* args);
 

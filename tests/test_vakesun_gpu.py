@@ -97,6 +97,54 @@ def test_token_gate_and_scaled_embedding(ctx, f32_table):
     np.testing.assert_array_equal(out.numpy(np.float32, (rows, stride)), table[toks] * np.float32(0.375))
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 90, 77), (1, 320, 2048), (5, 33, 200), (40, 130, 96), (100, 64, 64)])
+@pytest.mark.parametrize("f32_weights", [True, False])
+def test_product_epilogues_norm_add_next_norm_and_token_gate(ctx, m, n, k, f32_weights):
+    """The output projection of a sandwich sublayer in short passes: product -> Dynamic Tanh norm -> residual add with a factor -> the next
+    reader's norm, in the product's epilogue (one-row, few-row, tile and tensor-pipe kernels); and the token-gated gelu unit as an epilogue."""
+    rng = np.random.default_rng(m + n)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = bf16_exact(rng.standard_normal((n, k)) / 4)
+    pw, pb, nw, nb = (rng.standard_normal(n).astype(np.float32) for _ in range(4))
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    act = t64(x) if f32_weights or m < 32 else t64(bf16_exact(x))
+    y = act @ t64(w).T
+    updated = t64(res) + 0.3 * (torch.tanh(0.8 * y) * t64(pw) + t64(pb))
+    bx, bw = ctx.upload(x), ctx.upload(w if f32_weights else synth.f32_to_bf16_bits(w).reshape(w.shape))
+    dt = B.DT_F32 if f32_weights else B.DT_BF16
+    bpw, bpb, bnw, bnb, br, bo = ctx.upload(pw), ctx.upload(pb), ctx.upload(nw), ctx.upload(nb), ctx.upload(res), ctx.upload(np.zeros((m, n), np.float32))
+    a = B.DenseLinearArgs(a=bx.ptr, w=bw.ptr, d=br.ptr, m=m, n=n, k=k, lda=k, ldd=n, batch=1, weights_dt=dt, scale=1.0, post_weight=bpw.ptr, post_bias=bpb.ptr,
+                          next_weight=bnw.ptr, next_bias=bnb.ptr, next_out=bo.ptr, post_alpha=0.8, post_mult=0.3, next_alpha=1.4)
+    run(ctx, "uzu_dense_linear_encode", C.byref(a))
+    close(br.numpy(np.float32, (m, n)), updated.numpy(), 1e-5, "residual")
+    close(bo.numpy(np.float32, (m, n)), (torch.tanh(1.4 * updated) * t64(nw) + t64(nb)).numpy(), 1e-5, "next norm")
+    vocab, stride, column = 30, n + 7, 5
+    table = bf16_exact(rng.standard_normal((vocab, stride)))
+    toks = rng.integers(0, vocab, m).astype(np.uint32)
+    bt, bk, bd = ctx.upload(table if f32_weights else synth.f32_to_bf16_bits(table).reshape(table.shape)), ctx.upload(toks), ctx.upload(np.zeros((m, n), np.float32))
+    a = B.DenseLinearArgs(a=bx.ptr, w=bw.ptr, d=bd.ptr, m=m, n=n, k=k, lda=k, ldd=n, batch=1, weights_dt=dt, scale=1.0, token_ids=bk.ptr, token_table=bt.ptr,
+                          token_gate_dt=dt, token_table_stride=stride, token_column=column, token_vocab=vocab)
+    run(ctx, "uzu_dense_linear_encode", C.byref(a))
+    close(bd.numpy(np.float32, (m, n)), (P.gelu_tanh(y) * t64(table[toks, column:column + n])).numpy(), 1e-5, "token gate")
+
+
+def test_latent_prepare_norms_cache_row_and_query_latent_in_one_launch(ctx):
+    rng = np.random.default_rng(2)
+    rows, rank, q_rank, ld, prefix = 7, 27, 19, 60, 3
+    proj = (rng.standard_normal((rows, ld)) * 3).astype(np.float32)           # [query latent | kv latent | other]
+    cw = (1 + 0.3 * rng.standard_normal(rank)).astype(np.float32)
+    qw = (1 + 0.3 * rng.standard_normal(q_rank)).astype(np.float32)
+    bp, bcw, bqw = ctx.upload(proj), ctx.upload(cw), ctx.upload(qw)
+    cache, qo = ctx.upload(np.zeros((prefix + rows, rank), np.float32)), ctx.upload(np.zeros((rows, q_rank), np.float32))
+    a = B.LatentPrepareArgs(kv=bp.ptr + 4 * q_rank, cache=cache.ptr, latent_scales=bcw.ptr, rows=rows, heads=4, dim=8, rot_dim=0, rank=rank, kv_stride=ld,
+                            prefix=prefix, cache_dt=B.DT_F32, epsilon=1e-4, q_latent=bp.ptr, q_latent_scales=bqw.ptr, q_latent_out=qo.ptr, q_rank=q_rank, q_latent_stride=ld)
+    run(ctx, "uzu_latent_prepare_encode", C.byref(a))
+    got = cache.numpy(np.float32, (prefix + rows, rank))
+    assert not got[:prefix].any()
+    close(got[prefix:], (P.unit_rms(t64(proj[:, q_rank:q_rank + rank]), 1e-4) * t64(cw)).numpy(), 3e-6, "cache rows")
+    close(qo.numpy(np.float32, (rows, q_rank)), (P.unit_rms(t64(proj[:, :q_rank]), 1e-4) * t64(qw)).numpy(), 3e-6, "query latent")
+
+
 def rot_table(positions, rot):
     f, mult = P.rot_frequencies(rot)
     ang = np.arange(positions, dtype=np.float64)[:, None] * np.asarray(f, np.float64)[None, :]
@@ -717,7 +765,7 @@ def test_snapshot_and_restore_rewind_cache_and_states(ctx, tmp_path):
 
 def test_synthetic_checkpoint_of_a_preset_loads_and_decodes(ctx, tmp_path):
     """The benchmark's layer stack at a small width: the checkpoint writer's tensor names and shapes are the loader's."""
-    cfg = synth.vakesun_preset(width=256, vocab=300, blocks=1, ff=384, window=48, side_dim=16)
+    cfg = synth.vakesun_preset(width=256, vocab=300, layers=5, ff=384, window=48, side_dim=16, memory_ff=False)
     path = synth.write_vakesun_model(cfg, tmp_path / "preset", seed=1)
     w = {k: torch.from_numpy(np.asarray(synth.st_bits_to_f32(np.asarray(v))).reshape(v.shape).copy()) for k, v in st.load(path / "model.safetensors")[0].items()}
     toks = tokens_for(cfg, 90, 3)

@@ -136,7 +136,10 @@ DenseLinearArgs = _struct("uzu_dense_linear_args", [
     ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64), ("gate", u64), ("workspace", u64),
     ("m", u32), ("n", u32), ("k", u32), ("lda", u32), ("ldd", u32), ("batch", u32),
     ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("a_op", u32), ("gate_ld", u32), ("pair_rows", u32),
-    ("glu_limit", f32), ("glu_alpha", f32), ("glu_kind", u32), ("reserved0", u32), ("gate_bias", u64), ("col_scale", u64), ("row_scale", u64)])
+    ("glu_limit", f32), ("glu_alpha", f32), ("glu_kind", u32), ("reserved0", u32), ("gate_bias", u64), ("col_scale", u64), ("row_scale", u64),
+    ("post_weight", u64), ("post_bias", u64), ("next_weight", u64), ("next_bias", u64), ("next_out", u64),
+    ("post_alpha", f32), ("post_mult", f32), ("next_alpha", f32), ("token_gate_dt", u32), ("token_ids", u64), ("token_table", u64),
+    ("token_table_stride", u32), ("token_column", u32), ("token_vocab", u32), ("reserved2", u32)])
 
 GroupRmsNormArgs = _struct("uzu_group_rms_norm_args", [
     ("input", u64), ("scales", u64), ("output", u64), ("row_indices", u64),
@@ -161,7 +164,8 @@ LatentPrepareArgs = _struct("uzu_latent_prepare_args", [
     ("kv", u64), ("q", u64), ("query", u64), ("cache", u64), ("latent_scales", u64), ("cosines", u64), ("sines", u64),
     ("dynamic_position", u64),
     ("rows", u32), ("heads", u32), ("dim", u32), ("rot_dim", u32), ("rank", u32), ("rot_pairs", u32), ("kv_stride", u32),
-    ("q_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("reserved", u32)])
+    ("q_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("reserved", u32),
+    ("q_latent", u64), ("q_latent_scales", u64), ("q_latent_out", u64), ("q_rank", u32), ("q_latent_stride", u32)])
 
 LatentAttentionArgs = _struct("uzu_latent_attention_args", [
     ("query", u64), ("cache", u64), ("out", u64), ("dynamic_position", u64), ("partials", u64),

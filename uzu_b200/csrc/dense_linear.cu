@@ -56,6 +56,28 @@ __device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, floa
     }
     if (a.col_scale) v *= reinterpret_cast<const float*>(a.col_scale)[col];
     if (a.bias && z == 0) v += reinterpret_cast<const float*>(a.bias)[col];
+    if (a.post_weight) {          // sandwich epilogue: the product's own Dynamic Tanh norm, the residual add, the next reader's norm
+        float y = tanhf(a.post_alpha * v) * reinterpret_cast<const float*>(a.post_weight)[col];
+        if (a.post_bias) y += reinterpret_cast<const float*>(a.post_bias)[col];
+        const float x = fmaf(a.post_mult, y, *d);
+        *d = x;
+        if (a.next_out) {
+            float n = tanhf(a.next_alpha * x);
+            if (a.next_weight) n *= reinterpret_cast<const float*>(a.next_weight)[col];
+            if (a.next_bias) n += reinterpret_cast<const float*>(a.next_bias)[col];
+            reinterpret_cast<float*>(a.next_out)[(size_t)row * a.ldd + col] = n;
+        }
+        return;
+    }
+    if (a.token_table) {          // token-gate epilogue: gelu_tanh(product) * a table entry of the row's token
+        const uint32_t tok = reinterpret_cast<const uint32_t*>(a.token_ids)[row];
+        float e = 0.0f;
+        if (tok < a.token_vocab) {
+            const size_t at = (size_t)tok * a.token_table_stride + a.token_column + col;
+            e = a.token_gate_dt == UZU_DT_F32 ? reinterpret_cast<const float*>(a.token_table)[at] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.token_table)[at]);
+        }
+        v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) * e;
+    }
     if (a.accumulate) v += *d;
     *d = v;
 }
@@ -566,6 +588,12 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: unknown A operation, or a paired epilogue combined with gate / bias / accumulate");
         return;
     }
+    if ((a.post_weight && (a.accumulate || a.batch != 1 || a.pair_rows || a.token_table)) ||
+        (a.token_table && (!a.token_ids || a.pair_rows || a.batch != 1 || (a.token_gate_dt != UZU_DT_BF16 && a.token_gate_dt != UZU_DT_F32) ||
+                           a.token_column + a.n > a.token_table_stride))) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: the sandwich / token-gate epilogues take one plain product (no accumulate, no pairs, no batch)");
+        return;
+    }
     if (a.m == 0 || a.n == 0) return;
     if (a.lda == 0) a.lda = a.k;
     if (a.ldd == 0) a.ldd = a.n;
@@ -602,7 +630,7 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         cmd->record_error(UZU_ERROR_UNSUPPORTED, "dense_linear: the paired gated-unit epilogue covers passes of at most 8 rows");
         return;
     }
-    if (dense_umma_applicable(a)) {
+    if (!a.post_weight && !a.token_table && dense_umma_applicable(a)) {
         encode_dense_umma(cmd, a);
         return;
     }

@@ -548,6 +548,11 @@ struct uzu_engine {
         Buf sub_out;                                     // a sublayer's result before its own norm (sandwich layers)
         Buf token_factors;                               // per (token, head) decay, gain, floor and normaliser product of a gated matrix memory
         bool redirect = false;                           // the sublayer being encoded writes sub_out instead of adding into resid
+        // ... or, in short passes, its output projection's epilogue applies the sublayer's own norm, adds into resid and norms the
+        // updated stream for the next reader (`reader`, optional) by itself: no launch between the projection and the next sublayer
+        const Norm* fused_post = nullptr;
+        const Norm* fused_reader = nullptr;
+        float fused_mult = 1.0f;
         Buf resid, normed, operand_bf16, proj, lat, wide, lat_wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;

@@ -772,9 +772,11 @@ static void load_vakesun_model(uzu_engine* e, const Json& cfg, const std::string
                 append(in, read_floats(pl, p + "mix.dkv", {A.rank, W}));
                 rows += A.rank;
                 A.latent_norm = upload_f32(e, read_floats(pl, p + "mix.dkv.norm", {A.rank}).v);
-                kvb += (uint64_t)A.rank * storage_size(e->store_dt);
                 n_cache++;
             }
+            // bytes a decode step reads from the latent cache (the lender's rows, also for a borrower): the window's rows, or the whole context
+            if (A.window) stb += (uint64_t)A.window * A.rank * storage_size(e->store_dt);
+            else kvb += (uint64_t)A.rank * storage_size(e->store_dt);
             A.gate_offset = rows;
             append(in, read_floats(pl, p + "mix.g", {A.heads, W}));
             rows += A.heads;
@@ -958,6 +960,18 @@ static void encode_dense(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatr
     uzu_dense_linear_encode(cmd, &x);
 }
 
+// A sandwich layer's short pass: the output projection's epilogue norms the product, adds it into the residual stream and norms the
+// updated stream for the next reader (both norms are Dynamic Tanh, elementwise), instead of a launch of its own after the projection.
+static void sublayer_epilogue(uzu_engine* e, uzu_dense_linear_args& x) {
+    auto& P = e->pb;
+    if (!P.fused_post) return;
+    x.d = P.resid.ptr(); x.accumulate = 0;
+    x.post_weight = P.fused_post->scales.ptr(); x.post_bias = P.fused_post->bias.ptr(); x.post_alpha = P.fused_post->alpha; x.post_mult = P.fused_mult;
+    if (P.fused_reader) {
+        x.next_out = P.normed.ptr(); x.next_weight = P.fused_reader->scales.ptr(); x.next_bias = P.fused_reader->bias.ptr(); x.next_alpha = P.fused_reader->alpha;
+    }
+}
+
 // x += A . W^T: the sublayers' output projections add straight into the residual stream. With a sublayer gate the product is first
 // multiplied by scale[c] * sigmoid(logits[row, c] + bias[c]); the logits are columns [offset, offset + width) of a [rows, gate_ld] block.
 static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatrix& w, uint64_t a, uint32_t lda, uint32_t rows,
@@ -965,6 +979,7 @@ static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const D
     // (a sandwich layer's sublayer leaves its result in a scratch block: it goes through a norm of its own before it is added)
     uzu_dense_linear_args x = dense_args(e, w, a, rows, e->pb.redirect ? e->pb.sub_out.ptr() : e->pb.resid.ptr());
     x.lda = lda; x.accumulate = e->pb.redirect ? 0 : 1; x.a_op = a_op;
+    sublayer_epilogue(e, x);
     if (g && g->present) {
         if (g->bias.b) { x.gate = gate_block + (uint64_t)g->offset * 4; x.gate_ld = gate_ld; x.gate_bias = g->bias.ptr(); }
         if (g->scale.b) x.col_scale = g->scale.ptr();
@@ -1077,6 +1092,7 @@ static void encode_side_by_side(uzu_engine* e, uzu_command_buffer* cmd, const La
         uzu_dense_linear_args x = dense_args(e, A.out, P.mixed.ptr(), m, P.redirect ? P.sub_out.ptr() : P.resid.ptr());
         x.lda = A.heads * A.vdim; x.accumulate = P.redirect ? 0 : 1; x.scale = A.share;
         if (A.out_bias.b) x.bias = A.out_bias.ptr();
+        sublayer_epilogue(e, x);
         uzu_dense_linear_encode(cmd, &x);
     }
     if (L.has_retention()) {
@@ -1095,6 +1111,7 @@ static void encode_side_by_side(uzu_engine* e, uzu_command_buffer* cmd, const La
         uzu_head_norm_gate_encode(cmd, &na);
         uzu_dense_linear_args x = dense_args(e, R.out, P.gated_mix.ptr(), m, P.redirect ? P.sub_out.ptr() : P.resid.ptr());
         x.lda = rv; x.accumulate = (P.redirect && !L.has_window_attention()) ? 0 : 1; x.scale = R.share;       // the second of two mixers adds to the first
+        if (!L.has_window_attention()) sublayer_epilogue(e, x);
         uzu_dense_linear_encode(cmd, &x);
     }
 }
@@ -1133,11 +1150,14 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
     const uint32_t m = pc.m, ld = A.in.rows, qd = A.dim + A.rot_dim, width = A.rank + A.rot_dim;
     const uint64_t dyn = pc.dynamic ? e->decode_state.ptr() : 0;
     encode_dense(e, cmd, A.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [query latent | kv latent | rotated key | gate]; a borrower has no kv part
-    uzu_group_rms_norm_args qn{};
-    qn.input = P.proj.ptr(); qn.scales = A.q_norm.ptr(); qn.output = P.lat.ptr();
-    qn.rows = m; qn.n = A.q_rank; qn.groups = 1; qn.in_stride = ld; qn.out_stride = A.q_rank; qn.epsilon = e->norm_eps;
-    uzu_group_rms_norm_encode(cmd, &qn);
-    encode_dense(e, cmd, A.q_up, P.lat.ptr(), A.q_rank, m, P.wide.ptr());                  // q [m, heads, dim + rot_dim]
+    const bool q_norm_in_prepare = A.rot_dim == 0;      // without a rotated query part the prepare launch does not wait for q: it norms the query latent too
+    if (!q_norm_in_prepare) {
+        uzu_group_rms_norm_args qn{};
+        qn.input = P.proj.ptr(); qn.scales = A.q_norm.ptr(); qn.output = P.lat.ptr();
+        qn.rows = m; qn.n = A.q_rank; qn.groups = 1; qn.in_stride = ld; qn.out_stride = A.q_rank; qn.epsilon = e->norm_eps;
+        uzu_group_rms_norm_encode(cmd, &qn);
+        encode_dense(e, cmd, A.q_up, P.lat.ptr(), A.q_rank, m, P.wide.ptr());              // q [m, heads, dim + rot_dim]
+    }
     uzu_latent_prepare_args pa{};
     pa.kv = A.kv_from < 0 ? P.proj.ptr() + (uint64_t)A.kv_offset * 4 : 0; pa.q = A.rot_dim ? P.wide.ptr() : 0; pa.query = P.query.ptr(); pa.cache = S.keys;
     pa.latent_scales = A.latent_norm.ptr();
@@ -1148,10 +1168,9 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
     pa.dynamic_position = dyn;
     pa.rows = m; pa.heads = A.heads; pa.dim = A.dim; pa.rot_dim = A.rot_dim; pa.rank = A.rank; pa.kv_stride = ld; pa.q_stride = A.heads * qd;
     pa.prefix = S.length; pa.cache_dt = e->store_dt; pa.epsilon = e->norm_eps;
-    if (pa.kv || pa.q) {
-        if (!pa.q) pa.heads = 0;       // no rotated query part: only the cache row's unit runs
-        uzu_latent_prepare_encode(cmd, &pa);
-    }
+    if (q_norm_in_prepare) { pa.q_latent = P.proj.ptr(); pa.q_latent_scales = A.q_norm.ptr(); pa.q_latent_out = P.lat.ptr(); pa.q_rank = A.q_rank; pa.q_latent_stride = ld; }
+    if (pa.kv || pa.q || pa.q_latent) uzu_latent_prepare_encode(cmd, &pa);
+    if (q_norm_in_prepare) encode_dense(e, cmd, A.q_up, P.lat.ptr(), A.q_rank, m, P.wide.ptr());      // q [m, heads, dim]
     if (A.dim) {   // absorbed key projection, one z per head: query[:, h, 0:rank] = q[:, h, 0:dim] . (W_uk^h as [rank, dim])^T
         uzu_dense_linear_args x = dense_args(e, A.key_absorb, P.wide.ptr(), m, P.query.ptr());
         x.lda = A.heads * qd; x.ldd = A.heads * width; x.batch = A.heads;
@@ -1342,21 +1361,36 @@ static void encode_sandwich_layer(uzu_engine* e, uzu_command_buffer* cmd, const 
         if (reader) { a.output = P.normed.ptr(); set_norm(a, *reader, true); }
         uzu_norm_add_encode(cmd, &a);
     };
-    P.redirect = true;
-    encode_mixer(e, cmd, L, S, pc);
-    add(L.post_mixer, has_mlp ? &L.pre_mlp : (L.side.present ? nullptr : next));
-    if (has_mlp) {
-        encode_gated_mlp(e, cmd, L, pc, P.normed.ptr());
-        add(L.post_mlp, L.side.present ? nullptr : next);
-    }
-    P.redirect = false;
+    // Short passes (the decode step, short portions): a sublayer with ONE output projection and Dynamic Tanh norms around it takes the
+    // norm, the add and the next norm as that projection's epilogue. Long passes keep the projection on the tensor-memory kernel and add
+    // with a launch of their own.
+    const bool fuse = m < 128 && L.kind != MixSideBySide;
+    auto sublayer = [&](const Norm& post, const Norm* reader, auto&& encode) {
+        const bool fused = fuse && post.kind == 1 && (!reader || reader->kind == 1);
+        if (fused) { P.fused_post = &post; P.fused_reader = reader; P.fused_mult = L.residual_mult; }
+        else P.redirect = true;
+        encode();
+        P.fused_post = P.fused_reader = nullptr;
+        P.redirect = false;
+        if (!fused) add(post, reader);
+    };
+    sublayer(L.post_mixer, has_mlp ? &L.pre_mlp : (L.side.present ? nullptr : next), [&] { encode_mixer(e, cmd, L, S, pc); });
+    if (has_mlp) sublayer(L.post_mlp, L.side.present ? nullptr : next, [&] { encode_gated_mlp(e, cmd, L, pc, P.normed.ptr()); });
     if (L.side.present) {
         const TokenSide& T = L.side;
-        encode_dense(e, cmd, T.gate, P.resid.ptr(), W, m, P.lat.ptr());                  // the gate reads the residual stream itself
-        uzu_token_gate_args ta{};
-        ta.z = P.lat.ptr(); ta.token_ids = e->token_ids.ptr(); ta.table = e->pb_side_embed.w.ptr(); ta.out = P.lat.ptr();
-        ta.rows = m; ta.n = T.dim; ta.vocab = e->vocab; ta.table_stride = e->pb_side_embed.cols; ta.column = T.column; ta.weights_dt = e->store_dt;
-        uzu_token_gate_encode(cmd, &ta);
+        if (m < 128) {   // the gate reads the residual stream itself; in short passes its epilogue forms gelu_tanh(.) * the token's table entries
+            uzu_dense_linear_args x = dense_args(e, T.gate, P.resid.ptr(), m, P.lat.ptr());
+            x.lda = W;
+            x.token_ids = e->token_ids.ptr(); x.token_table = e->pb_side_embed.w.ptr(); x.token_gate_dt = e->store_dt;
+            x.token_table_stride = e->pb_side_embed.cols; x.token_column = T.column; x.token_vocab = e->vocab;
+            uzu_dense_linear_encode(cmd, &x);
+        } else {         // long passes: the product on the tensor-memory kernel, then the unit
+            encode_dense(e, cmd, T.gate, P.resid.ptr(), W, m, P.lat.ptr());
+            uzu_token_gate_args ta{};
+            ta.z = P.lat.ptr(); ta.token_ids = e->token_ids.ptr(); ta.table = e->pb_side_embed.w.ptr(); ta.out = P.lat.ptr();
+            ta.rows = m; ta.n = T.dim; ta.vocab = e->vocab; ta.table_stride = e->pb_side_embed.cols; ta.column = T.column; ta.weights_dt = e->store_dt;
+            uzu_token_gate_encode(cmd, &ta);
+        }
         encode_dense(e, cmd, T.proj, P.lat.ptr(), T.dim, m, P.sub_out.ptr());
         Norm rms;
         rms.kind = 0; rms.scales = T.norm;

@@ -29,7 +29,18 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const uzu_latent_pr
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[32];
-    const uint32_t t = blockIdx.x, unit = blockIdx.y;        // unit 0: the cache row; unit 1 + h: the rotated part of head h's query
+    const uint32_t t = blockIdx.x, unit = blockIdx.y;        // unit 0: the cache row; unit 1 + h: the rotated part of head h's query; the last unit: the query latent's norm
+    if (a.q_latent && unit == gridDim.y - 1) {
+        const float* x = reinterpret_cast<const float*>(a.q_latent) + (size_t)t * a.q_latent_stride;
+        float* out = reinterpret_cast<float*>(a.q_latent_out) + (size_t)t * a.q_rank;
+        const float* sc = reinterpret_cast<const float*>(a.q_latent_scales);
+        float ss = 0.0f;
+        for (uint32_t i = threadIdx.x; i < a.q_rank; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)a.q_rank + a.epsilon);
+        for (uint32_t i = threadIdx.x; i < a.q_rank; i += blockDim.x) out[i] = x[i] * inv * (sc ? sc[i] : 1.0f);
+        return;
+    }
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
     const uint32_t pos = prefix + t;
     const uint32_t width = a.rank + a.rot_dim;
@@ -276,7 +287,9 @@ static void launch_latent_attention(uzu_command_buffer* cmd, const uzu_latent_at
     const uint32_t width = a.rank + a.rot_dim;
     const size_t smem = ((size_t)LA_HEADS * width + 4 + (size_t)LA_KEYS * width) * sizeof(float);
     static std::atomic<uint64_t> done{0};
-    if (smem > 48 * 1024) opt_in_dynamic_smem(cmd, latent_attention_kernel<T, RV>, (int)smem, done);
+    // the opt-in is made once per instance and device, so it asks for the widest row the entry point accepts (models of different row
+    // widths may share an instance in one process)
+    if (smem > 48 * 1024) opt_in_dynamic_smem(cmd, latent_attention_kernel<T, RV>, 201 * 1024, done);
     const uint32_t splits = (a.splits > 1 && a.partials) ? std::min(a.splits, 64u) : 1;
     dim3 grid(a.rows, (a.heads + LA_HEADS - 1) / LA_HEADS, splits);
     launch(cmd, "latent_attention_kernel", latent_attention_kernel<T, RV>, grid, dim3(LA_HEADS * 32), smem, a);
@@ -302,14 +315,17 @@ using namespace uzu;
 
 void uzu_latent_prepare_encode(uzu_command_buffer* cmd, const uzu_latent_prepare_args* a) {
     if (!encodable(cmd, "latent_prepare")) return;
-    if ((!a->kv && !a->q) || (a->kv && !a->cache) || (a->q && !a->query) || (a->rot_pairs && (!a->cosines || !a->sines)) || 2 * a->rot_pairs > a->rot_dim ||
+    if ((!a->kv && !a->q && !a->q_latent) || (a->q_latent && (!a->q_latent_out || !a->q_rank)) || (a->kv && !a->cache) || (a->q && !a->query) || (a->rot_pairs && (!a->cosines || !a->sines)) || 2 * a->rot_pairs > a->rot_dim ||
         (a->cache_dt != UZU_DT_BF16 && a->cache_dt != UZU_DT_F32)) {
         cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "latent_prepare: inconsistent arguments");
         return;
     }
     if (a->rows == 0) return;
-    if (a->cache_dt == UZU_DT_BF16) launch(cmd, "latent_prepare_kernel", latent_prepare_kernel<__nv_bfloat16>, dim3(a->rows, 1 + a->heads), dim3(128), 0, *a);
-    else launch(cmd, "latent_prepare_kernel", latent_prepare_kernel<float>, dim3(a->rows, 1 + a->heads), dim3(128), 0, *a);
+    uzu_latent_prepare_args b = *a;
+    if (!b.q_latent_stride) b.q_latent_stride = b.q_rank;
+    const dim3 grid(b.rows, 1 + (b.q ? b.heads : 0) + (b.q_latent ? 1 : 0));      // without rotated query parts the heads' units are not launched
+    if (b.cache_dt == UZU_DT_BF16) launch(cmd, "latent_prepare_kernel", latent_prepare_kernel<__nv_bfloat16>, grid, dim3(128), 0, b);
+    else launch(cmd, "latent_prepare_kernel", latent_prepare_kernel<float>, grid, dim3(128), 0, b);
 }
 
 void uzu_latent_attention_encode(uzu_command_buffer* cmd, const uzu_latent_attention_args* a) {

@@ -730,17 +730,22 @@ def write_vakesun_model(config: dict, path, seed: int = 0, tensors: dict | None 
     return write_punilix_model(config, path, seed, tensors if tensors is not None else vakesun_tensors(config, seed))
 
 
-def vakesun_preset(width=2048, vocab=32768, blocks=3, ff=None, window=512, side_dim=256) -> dict:
-    """A layer stack of realistic sizes for benchmarks: per block a windowed latent-attention layer, a full attention layer, a matrix-memory
-    layer without feed-forward and a second latent-attention layer that reads the first one's latents."""
+def vakesun_preset(width=2048, vocab=32768, layers=8, ff=None, window=512, side_dim=256, memory_ff=True) -> dict:
+    """A layer stack of realistic sizes for benchmarks, `layers` layers in the order: a windowed latent-attention layer, a full attention
+    layer with grouped key / value heads, a matrix-memory layer (with a feed-forward only when memory_ff), a second latent-attention layer
+    that reads the first one's latents; then again."""
     ff = ff or 4 * width
     heads = max(width // 128, 1)
     yarn = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
-    layers = []
-    for b in range(blocks):
-        first = len(layers)
-        layers.append(vakesun_latent_layer(heads, 128, 128, 512, min(1536, width), window, vakesun_dense_mlp(ff)))
-        layers.append(vakesun_attention_layer(heads, max(heads // 4, 1), 128, 128, vakesun_dense_mlp(ff), rot_dims=64, rot_base=1e6, scaling=yarn))
-        layers.append(vakesun_mlstm_layer(max(heads // 2, 1), 128, 128, None))
-        layers.append(vakesun_latent_layer(heads, 128, 128, 512, min(1536, width), window, vakesun_dense_mlp(ff), kv_from=first))
-    return vakesun_config(width, vocab, layers, eps=1e-6, residual_mult=0.3, embedding_scale=1.0, side_dim=side_dim)
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            out.append(vakesun_latent_layer(heads, 128, 128, 512, min(1536, width), window, vakesun_dense_mlp(ff)))
+        elif kind == 1:
+            out.append(vakesun_attention_layer(heads, max(heads // 4, 1), 128, 128, vakesun_dense_mlp(ff), rot_dims=64, rot_base=1e6, scaling=yarn))
+        elif kind == 2:
+            out.append(vakesun_mlstm_layer(heads, 128, 128, vakesun_dense_mlp(ff) if memory_ff else None))
+        else:
+            out.append(vakesun_latent_layer(heads, 128, 128, 512, min(1536, width), window, vakesun_dense_mlp(ff), kv_from=i - 3))
+    return vakesun_config(width, vocab, out, eps=1e-6, residual_mult=0.3, embedding_scale=1.0, side_dim=side_dim)
