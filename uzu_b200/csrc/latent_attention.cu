@@ -34,11 +34,26 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const uzu_latent_pr
         const float* x = reinterpret_cast<const float*>(a.q_latent) + (size_t)t * a.q_latent_stride;
         float* out = reinterpret_cast<float*>(a.q_latent_out) + (size_t)t * a.q_rank;
         const float* sc = reinterpret_cast<const float*>(a.q_latent_scales);
+        constexpr int KEEP = 8;        // the row's elements and weights are requested at once and stay in registers between the sum and the scaling
+        float v[KEEP], w[KEEP];
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            v[j] = i < a.q_rank ? x[i] : 0.0f;
+            w[j] = (i < a.q_rank && sc) ? sc[i] : 1.0f;
+        }
         float ss = 0.0f;
-        for (uint32_t i = threadIdx.x; i < a.q_rank; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) ss = fmaf(v[j], v[j], ss);
+        for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < a.q_rank; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)a.q_rank + a.epsilon);
-        for (uint32_t i = threadIdx.x; i < a.q_rank; i += blockDim.x) out[i] = x[i] * inv * (sc ? sc[i] : 1.0f);
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            if (i < a.q_rank) out[i] = v[j] * inv * w[j];
+        }
+        for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < a.q_rank; i += blockDim.x) out[i] = x[i] * inv * (sc ? sc[i] : 1.0f);
         return;
     }
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
@@ -51,11 +66,25 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const uzu_latent_pr
         const float* kv = reinterpret_cast<const float*>(a.kv) + (size_t)t * a.kv_stride;
         T* row = reinterpret_cast<T*>(a.cache) + (size_t)pos * width;
         const float* sc = reinterpret_cast<const float*>(a.latent_scales);
+        float v[4], w[4];              // rank <= 512 = 4 x 128 threads: the latent and its weights are requested at once
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            v[j] = i < a.rank ? kv[i] : 0.0f;
+            w[j] = (i < a.rank && sc) ? sc[i] : 1.0f;
+        }
         float ss = 0.0f;
-        for (uint32_t i = threadIdx.x; i < a.rank; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss = fmaf(v[j], v[j], ss);
+        for (uint32_t i = threadIdx.x + 4 * blockDim.x; i < a.rank; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)a.rank + a.epsilon);
-        for (uint32_t i = threadIdx.x; i < a.rank; i += blockDim.x) cache_store<T>(row + i, kv[i] * inv * (sc ? sc[i] : 1.0f));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t i = threadIdx.x + j * blockDim.x;
+            if (i < a.rank) cache_store<T>(row + i, v[j] * inv * w[j]);
+        }
+        for (uint32_t i = threadIdx.x + 4 * blockDim.x; i < a.rank; i += blockDim.x) cache_store<T>(row + i, kv[i] * inv * (sc ? sc[i] : 1.0f));
         for (uint32_t i = threadIdx.x; i < a.rot_pairs; i += blockDim.x) {
             const float x0 = kv[a.rank + 2 * i], x1 = kv[a.rank + 2 * i + 1], c = cosr[i], s = sinr[i];
             cache_store<T>(row + a.rank + 2 * i, x0 * c - x1 * s);

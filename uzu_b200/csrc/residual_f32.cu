@@ -54,6 +54,25 @@ __device__ __forceinline__ float norm_add_value(uint32_t kind, float x, float in
     return v;
 }
 
+// Dynamic Tanh in and (if any) out: nothing crosses an element, so the work is cut over elements, not rows.
+__global__ void __launch_bounds__(256) norm_add_elementwise_kernel(const uzu_norm_add_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t row = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= a.n) return;
+    const float* w = reinterpret_cast<const float*>(a.weight);
+    const float* b = reinterpret_cast<const float*>(a.bias);
+    const float v = norm_add_value(1, reinterpret_cast<const float*>(a.input)[(size_t)row * a.in_stride + i], 1.0f, a.alpha, w, b, i);
+    float* out = a.output ? reinterpret_cast<float*>(a.output) + (size_t)row * a.n : nullptr;
+    if (!a.residual) { out[i] = v; return; }
+    float* res = reinterpret_cast<float*>(a.residual) + (size_t)row * a.n;
+    const float x = fmaf(a.mult, v, res[i]);
+    res[i] = x;
+    if (out) out[i] = norm_add_value(1, x, 1.0f, a.next_alpha, reinterpret_cast<const float*>(a.next_weight), reinterpret_cast<const float*>(a.next_bias), i);
+}
+
+// One CTA per row; a thread keeps up to KEEP of the row's elements (input, weights, residual) in registers, all requested before the
+// first sum, so a decode step's single row costs one round trip to memory and not one per pass over the row.
 __global__ void __launch_bounds__(256) norm_add_kernel(const uzu_norm_add_args a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -62,39 +81,64 @@ __global__ void __launch_bounds__(256) norm_add_kernel(const uzu_norm_add_args a
     const float* in = reinterpret_cast<const float*>(a.input) + (size_t)row * a.in_stride;
     const float* w = reinterpret_cast<const float*>(a.weight);
     const float* b = reinterpret_cast<const float*>(a.bias);
+    const float* nw = reinterpret_cast<const float*>(a.next_weight);
+    const float* nb = reinterpret_cast<const float*>(a.next_bias);
+    float* res = a.residual ? reinterpret_cast<float*>(a.residual) + (size_t)row * a.n : nullptr;
+    float* out = a.output ? reinterpret_cast<float*>(a.output) + (size_t)row * a.n : nullptr;
+    constexpr int KEEP = 8;
+    float x[KEEP], wv[KEEP], bv[KEEP], rv[KEEP], nwv[KEEP], nbv[KEEP];
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        const bool ok = i < a.n;
+        x[j] = ok ? in[i] : 0.0f;
+        wv[j] = (ok && w) ? w[i] : 1.0f;
+        bv[j] = (ok && b) ? b[i] : 0.0f;
+        rv[j] = (ok && res) ? res[i] : 0.0f;
+        nwv[j] = (ok && nw) ? nw[i] : 1.0f;
+        nbv[j] = (ok && nb) ? nb[i] : 0.0f;
+    }
     float inv = 1.0f;
     if (a.kind == 0) {
         float ss = 0.0f;
-        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) ss = fmaf(x[j], x[j], ss);
+        for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < a.n; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
         ss = block_sum(ss, red);
         inv = 1.0f / sqrtf(ss / (float)a.n + a.epsilon);
     }
-    float* out = a.output ? reinterpret_cast<float*>(a.output) + (size_t)row * a.n : nullptr;
-    if (!a.residual) {
-        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) out[i] = norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i);
-        return;
-    }
-    float* res = reinterpret_cast<float*>(a.residual) + (size_t)row * a.n;
-    const float* nw = reinterpret_cast<const float*>(a.next_weight);
-    const float* nb = reinterpret_cast<const float*>(a.next_bias);
-    if (!out || a.next_kind == 1) {
-        for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) {
-            const float x = fmaf(a.mult, norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i), res[i]);
-            res[i] = x;
-            if (out) out[i] = norm_add_value(1, x, 1.0f, a.next_alpha, nw, nb, i);
+    // first norm, and the residual add
+    float ss2 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        float v = (a.kind == 1 ? tanhf(a.alpha * x[j]) : x[j] * inv) * wv[j] + bv[j];
+        if (res) v = fmaf(a.mult, v, rv[j]);
+        x[j] = v;
+        if (i < a.n) {
+            ss2 = fmaf(v, v, ss2);
+            if (res) res[i] = v;
+            else out[i] = v;
         }
-        return;
     }
-    float ss = 0.0f;
-    for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) {
-        const float x = fmaf(a.mult, norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i), res[i]);
-        res[i] = x;           // read back below by the thread that wrote it
-        ss = fmaf(x, x, ss);
+    for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < a.n; i += blockDim.x) {
+        float v = norm_add_value(a.kind, in[i], inv, a.alpha, w, b, i);
+        if (res) { v = fmaf(a.mult, v, res[i]); res[i] = v; }          // read back below by the thread that wrote it
+        else out[i] = v;
+        ss2 = fmaf(v, v, ss2);
     }
-    __syncthreads();          // `red` is free again
-    ss = block_sum(ss, red);
-    const float inv2 = 1.0f / sqrtf(ss / (float)a.n + a.epsilon);
-    for (uint32_t i = threadIdx.x; i < a.n; i += blockDim.x) out[i] = norm_add_value(0, res[i], inv2, 0.0f, nw, nb, i);
+    if (!res || !out) return;
+    float inv2 = 1.0f;
+    if (a.next_kind == 0) {
+        ss2 = block_sum(ss2, red);
+        inv2 = 1.0f / sqrtf(ss2 / (float)a.n + a.epsilon);
+    }
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        if (i < a.n) out[i] = (a.next_kind == 1 ? tanhf(a.next_alpha * x[j]) : x[j] * inv2) * nwv[j] + nbv[j];
+    }
+    for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < a.n; i += blockDim.x) out[i] = norm_add_value(a.next_kind, res[i], inv2, a.next_alpha, nw, nb, i);
 }
 
 template <typename TW>
@@ -431,7 +475,10 @@ void uzu_norm_add_encode(uzu_command_buffer* cmd, const uzu_norm_add_args* a) {
     if (a->rows == 0 || a->n == 0) return;
     uzu_norm_add_args b = *a;
     if (!b.in_stride) b.in_stride = b.n;
-    launch(cmd, "norm_add_kernel", norm_add_kernel, dim3(b.rows), dim3(256), 0, b);
+    if (b.kind == 1 && (!b.residual || !b.output || b.next_kind == 1))
+        launch(cmd, "norm_add_elementwise_kernel", norm_add_elementwise_kernel, dim3((b.n + 255) / 256, b.rows), dim3(256), 0, b);
+    else
+        launch(cmd, "norm_add_kernel", norm_add_kernel, dim3(b.rows), dim3(256), 0, b);
 }
 
 void uzu_token_gate_encode(uzu_command_buffer* cmd, const uzu_token_gate_args* a) {
