@@ -495,7 +495,9 @@ typedef struct uzu_dense_linear_args {
     float post_alpha, post_mult, next_alpha;
     uint32_t token_gate_dt;        /* token-gate epilogue (token_table != 0): D = gelu_tanh(y) * token_table[token_ids[row], token_column + col], */
     uint64_t token_ids, token_table;   /* token_table of type token_gate_dt [vocab, token_table_stride], token_ids u32 [rows] (ids >= token_vocab read 0) */
-    uint32_t token_table_stride, token_column, token_vocab, reserved2;
+    uint32_t token_table_stride, token_column, token_vocab;
+    uint32_t a_bf16;               /* 1: A is bf16 [m, k] (lda = k, 16-byte aligned), e.g. rows of a bf16 cache; only the tcgen05 form takes it
+                                      (bf16 weights, batch 1, m >= 128, k a multiple of 64, n >= 64), no A operation */
 } uzu_dense_linear_args;
 UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
 /* 0, or the code of the first bounded barrier wait that ran out inside a tensor-memory dense product (the kernel gives up and returns) */
@@ -535,6 +537,8 @@ typedef struct uzu_token_gate_args {
     uint32_t rows, n, vocab, table_stride, column, weights_dt;
 } uzu_token_gate_args;
 UZU_API void uzu_token_gate_encode(uzu_command_buffer* cmd, const uzu_token_gate_args* args);
+/* bf16 copy of a column range of f32 rows: dst[r, 0:n] = bf16(src[r, 0:n]) (src rows src_stride apart, dst rows dense) */
+UZU_API void uzu_rows_to_bf16_encode(uzu_command_buffer* cmd, uint64_t src, uint32_t src_stride, uint64_t dst, uint32_t rows, uint32_t n);
 
 /* Elementwise glue, all f32.
  *   embedding_f32:   out[r, :] = table[token[r], :] (table weights_dt [vocab, n])
@@ -758,7 +762,9 @@ typedef struct uzu_window_attention_args {
     uint64_t tickets;              /* scratch u32 [rows*heads], zero before the first use */
     uint32_t rows, heads, kv_heads, dim, vdim, prefix, cache_dt, window, keep_first, v_pairs;
     float scale, softcap;
-    uint32_t splits, reserved;
+    uint32_t splits, head_gate_stride;
+    uint64_t sinks;                /* optional f32 [heads]: the softmax denominator also holds exp(sinks[h]) (no key, no value, not scaled) */
+    uint64_t head_gate;            /* optional f32 [rows, head_gate_stride]: head h's output is multiplied by sigmoid(head_gate[t, h]) */
 } uzu_window_attention_args;
 UZU_API void uzu_window_attention_encode(uzu_command_buffer* cmd, const uzu_window_attention_args* args);
 

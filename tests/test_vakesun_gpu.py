@@ -216,6 +216,56 @@ def test_attention_with_half_split_rotation(ctx, T, prefix, heads, kv_heads, dim
         close(got, ref[prefix:], 3e-5 if f32_cache else 1e-2, f"splits {splits}")
 
 
+@pytest.mark.parametrize("T,prefix,heads,dim,vdim,window", [(40, 0, 3, 16, 24, 7), (200, 0, 4, 64, 32, 70), (150, 130, 2, 128, 128, 50), (70, 64, 2, 16, 16, 0), (5, 90, 2, 10, 6, 33)])
+@pytest.mark.parametrize("f32_cache", [True, False])
+def test_softmax_attention_with_sink_and_head_gate(ctx, T, prefix, heads, dim, vdim, window, f32_cache):
+    """The window-attention kernels (plain with key splits, and the tensor-pipe one for bf16 passes of >= 64 rows) with a sink term per head
+    and a sigmoid gate per head, as the expanded form of latent attention uses them; the caches are addressed from a later row on (the
+    pointer names where row 0 WOULD be), as a temporary copy of the visible range is."""
+    rng = np.random.default_rng(T + dim)
+    n = prefix + T
+    q = rng.standard_normal((n, heads, dim)).astype(np.float32)
+    k, v = rng.standard_normal((n, heads, dim)).astype(np.float32), rng.standard_normal((n, heads, vdim)).astype(np.float32)
+    if not f32_cache:
+        k, v = bf16_exact(k), bf16_exact(v)
+    sink = (rng.standard_normal(heads) * 2).astype(np.float32)
+    gate = (rng.standard_normal((n, heads + 2)) * 2).astype(np.float32)
+    pos = list(range(n))
+    ref = (P.softmax_attention(t64(q), t64(k), t64(v), pos, pos, 0.3, window=window, sink=t64(sink)) * torch.sigmoid(t64(gate[:, :heads]))[:, :, None]).numpy()
+    lo = (max(0, prefix + 1 - window) if window else 0) // 64 * 64
+    as_cache = (lambda x: x) if f32_cache else (lambda x: synth.f32_to_bf16_bits(x).reshape(x.shape))
+    bk, bv = ctx.upload(as_cache(k[lo:].reshape(n - lo, -1))), ctx.upload(as_cache(v[lo:].reshape(n - lo, -1)))
+    size = 4 if f32_cache else 2
+    bq, bs, bg = ctx.upload(q[prefix:]), ctx.upload(sink), ctx.upload(gate[prefix:])
+    for splits in (1, 3):
+        out, parts, tickets = ctx.upload(np.zeros((T, heads * vdim), np.float32)), ctx.upload(np.zeros(T * heads * splits * (vdim + 2), np.float32)), ctx.upload(np.zeros(T * heads, np.uint32))
+        a = B.WindowAttentionArgs(query=bq.ptr, keys=bk.ptr - lo * heads * dim * size, values=bv.ptr - lo * heads * vdim * size, out=out.ptr, partials=parts.ptr,
+                                  tickets=tickets.ptr, rows=T, heads=heads, kv_heads=heads, dim=dim, vdim=vdim, prefix=prefix,
+                                  cache_dt=B.DT_F32 if f32_cache else B.DT_BF16, window=window, scale=0.3, splits=splits, sinks=bs.ptr, head_gate=bg.ptr,
+                                  head_gate_stride=heads + 2)
+        run(ctx, "uzu_window_attention_encode", C.byref(a))
+        # (the tensor-pipe kernel carries query and weights as two bf16 numbers each: 2^-16 relative)
+        close(out.numpy(np.float32, (T, heads, vdim)), ref[prefix:], 3e-5 if f32_cache else 1e-4, f"splits {splits}")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (300, 200, 192), (1000, 96, 512)])
+def test_product_of_bf16_rows_on_tensor_memory_and_bf16_copy(ctx, m, n, k):
+    """A = rows of a bf16 cache, read as they are by the tensor-memory product; the f32 result copied to bf16 column ranges."""
+    rng = np.random.default_rng(m)
+    x, w = bf16_exact(rng.standard_normal((m, k))), bf16_exact(rng.standard_normal((n, k)) / 8)
+    bx, bw = ctx.upload(synth.f32_to_bf16_bits(x).reshape(x.shape)), ctx.upload(synth.f32_to_bf16_bits(w).reshape(w.shape))
+    bd, ws = ctx.upload(np.zeros((m, n), np.float32)), ctx.upload(np.zeros(16, np.uint16))
+    a = B.DenseLinearArgs(a=bx.ptr, w=bw.ptr, d=bd.ptr, workspace=ws.ptr, m=m, n=n, k=k, lda=k, ldd=n, batch=1, weights_dt=B.DT_BF16, scale=1.0, a_bf16=1)
+    run(ctx, "uzu_dense_linear_encode", C.byref(a))
+    ref = (t64(x) @ t64(w).T).numpy()
+    close(bd.numpy(np.float32, (m, n)), ref, 5e-6, "product")
+    assert ctx.lib.uzu_debug_dense_umma_error() == 0
+    half = n // 2
+    bo = ctx.upload(np.zeros((m, n - half), np.uint16))
+    run(ctx, "uzu_rows_to_bf16_encode", bd.ptr + 4 * half, n, bo.ptr, m, n - half)
+    np.testing.assert_array_equal(bo.numpy(np.uint16, (m, n - half)), synth.f32_to_bf16_bits(bd.numpy(np.float32, (m, n))[:, half:]).reshape(m, n - half))
+
+
 def test_rotation_layout_is_halves_not_neighbours(ctx):
     """One query / key pair with a single non-zero channel each: under the half-split layout channel 0 pairs with channel dims / 2."""
     dim, rot = 8, {"base": 10.0, "dims": 8}
@@ -472,6 +522,18 @@ def config_c():
     ], eps=1e-5, residual_mult=0.7, embedding_scale=2.0, side_dim=3)
 
 
+def config_d():
+    """Latent sizes the expanded prompt form takes (latent 64 / 128, head sizes in multiples of 16): windows shorter and longer than a pass,
+    a borrower with other head sizes than its lender, no window at all."""
+    return P.make_config(128, 150, [
+        P.latent_layer(4, 16, 32, 64, 24, 20, 40),
+        P.mlstm_layer(2, 16, 16, None),
+        P.latent_layer(2, 32, 16, 64, 16, 100, 24, kv_from=0),
+        P.latent_layer(3, 16, 16, 128, 32, 100000, None),
+        P.attention_layer(4, 2, 32, 16, 36, rot_dims=16, base=1e4),
+    ], eps=1e-5, residual_mult=0.4, embedding_scale=1.0, side_dim=16)
+
+
 def write_model(path, config, weights):
     path.mkdir(parents=True, exist_ok=True)
     (path / "config.json").write_text(json.dumps(config))
@@ -515,11 +577,11 @@ def tokens_for(config, n, seed=0):
     return np.random.default_rng(seed).integers(0, config["vocab"], n).tolist()
 
 
-@pytest.mark.parametrize("make", [config_a, config_b, config_c])
+@pytest.mark.parametrize("make", [config_a, config_b, config_c, config_d])
 @pytest.mark.parametrize("f32", [True, False])
 def test_prompt_logits_and_layers(ctx, tmp_path, make, f32):
     pr = Pair(ctx, tmp_path, make(), seed=1, f32=f32)
-    toks = tokens_for(pr.config, 70 if f32 else 150, 1)     # bf16: 150 rows take the tensor-pipe products and attention
+    toks = tokens_for(pr.config, 70 if f32 else 150, 1)     # bf16: 150 rows take the tensor-pipe products and attention (and expanded latents)
     pr.engine.debug_layer_outputs(True)
     s = pr.engine.slot_acquire()
     got = pr.engine.forward_rows(toks, list(range(len(toks))), slot=s)
@@ -534,7 +596,7 @@ def test_prompt_logits_and_layers(ctx, tmp_path, make, f32):
     pr.close()
 
 
-@pytest.mark.parametrize("make", [config_a, config_b, config_c])
+@pytest.mark.parametrize("make", [config_a, config_b, config_c, config_d])
 @pytest.mark.parametrize("f32", [True, False])
 def test_decode_and_portions_match_the_whole_prompt(ctx, tmp_path, make, f32):
     """Prefill + token-by-token decoding (the windows pass over decoded tokens), and portions of 2, 3, 1, 33, 2, ... tokens cut in the middle
@@ -560,6 +622,10 @@ def test_decode_and_portions_match_the_whole_prompt(ctx, tmp_path, make, f32):
     s = pr.engine.slot_acquire()                 # from the very first token one by one
     parts = [pr.engine.forward_rows(toks[p:p + 1], [0], slot=s) for p in range(30)]
     pr.check(np.concatenate(parts), ref[:30], "one by one from the start")
+    pr.engine.slot_release(s)
+    s = pr.engine.slot_acquire()                 # long portions after a prefix: 90 + 80 rows see windows that start before their pass
+    parts = [pr.engine.forward_rows(toks[:90], list(range(90)), slot=s), pr.engine.forward_rows(toks[90:], list(range(n - 90)), slot=s)]
+    pr.check(np.concatenate(parts), ref, "two long portions")
     pr.close()
 
 

@@ -139,7 +139,7 @@ DenseLinearArgs = _struct("uzu_dense_linear_args", [
     ("glu_limit", f32), ("glu_alpha", f32), ("glu_kind", u32), ("reserved0", u32), ("gate_bias", u64), ("col_scale", u64), ("row_scale", u64),
     ("post_weight", u64), ("post_bias", u64), ("next_weight", u64), ("next_bias", u64), ("next_out", u64),
     ("post_alpha", f32), ("post_mult", f32), ("next_alpha", f32), ("token_gate_dt", u32), ("token_ids", u64), ("token_table", u64),
-    ("token_table_stride", u32), ("token_column", u32), ("token_vocab", u32), ("reserved2", u32)])
+    ("token_table_stride", u32), ("token_column", u32), ("token_vocab", u32), ("a_bf16", u32)])
 
 GroupRmsNormArgs = _struct("uzu_group_rms_norm_args", [
     ("input", u64), ("scales", u64), ("output", u64), ("row_indices", u64),
@@ -224,7 +224,7 @@ WindowAttentionArgs = _struct("uzu_window_attention_args", [
     ("query", u64), ("keys", u64), ("values", u64), ("out", u64), ("dynamic_position", u64), ("head_temp", u64),
     ("v_cosines", u64), ("v_sines", u64), ("partials", u64), ("tickets", u64),
     ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("prefix", u32), ("cache_dt", u32), ("window", u32),
-    ("keep_first", u32), ("v_pairs", u32), ("scale", f32), ("softcap", f32), ("splits", u32), ("reserved", u32)])
+    ("keep_first", u32), ("v_pairs", u32), ("scale", f32), ("softcap", f32), ("splits", u32), ("head_gate_stride", u32), ("sinks", u64), ("head_gate", u64)])
 
 MAIN_SLOT = 0xFFFFFFFF
 
@@ -262,7 +262,7 @@ uzu_general_delta_encode uzu_head_norm_gate_encode uzu_latent_prepare_encode uzu
 uzu_silu_glu_encode uzu_topk_route_encode uzu_routed_combine_gated_encode uzu_sigmoid_attention_prepare_encode uzu_sigmoid_attention_encode
 uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs uzu_debug_dense_umma_error
 uzu_min_gru_encode uzu_retention_encode uzu_window_attention_prepare_encode uzu_window_attention_encode
-uzu_exp_gates_encode uzu_norm_add_encode uzu_token_gate_encode uzu_embedding_f32_scaled_encode""".split()
+uzu_exp_gates_encode uzu_norm_add_encode uzu_token_gate_encode uzu_embedding_f32_scaled_encode uzu_rows_to_bf16_encode""".split()
 
 _lib = None
 
@@ -420,6 +420,7 @@ def load() -> C.CDLL:
         "uzu_exp_gates_encode": (None, [vp, C.POINTER(ExpGatesArgs)]),
         "uzu_norm_add_encode": (None, [vp, C.POINTER(NormAddArgs)]),
         "uzu_token_gate_encode": (None, [vp, C.POINTER(TokenGateArgs)]),
+        "uzu_rows_to_bf16_encode": (None, [vp, u64, u32, u64, u32, u32]),
         "uzu_embedding_f32_scaled_encode": (None, [vp, u64, u64, u32, u64, u32, u32, u32, f32]),
         "uzu_engine_slot_acquire": (C.c_int, [vp, C.POINTER(u32)]),
         "uzu_engine_slot_release": (C.c_int, [vp, u32]),

@@ -595,6 +595,16 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         return;
     }
     if (a.m == 0 || a.n == 0) return;
+    if (a.a_bf16) {      // A rows that are bf16 already (a cache's rows): the tensor-memory form reads them as they are
+        const bool dense_rows = a.lda == 0 || a.lda == a.k;
+        a.lda = a.k;
+        if (!dense_rows || a.a_op || a.post_weight || a.token_table || !dense_umma_applicable(a)) {
+            cmd->record_error(UZU_ERROR_UNSUPPORTED, "dense_linear: bf16 activations need the tcgen05 form (bf16 weights, dense rows, a workspace pointer, m >= 128, k a multiple of 64, n >= 64, no A operation)");
+            return;
+        }
+        encode_dense_umma(cmd, a);
+        return;
+    }
     if (a.lda == 0) a.lda = a.k;
     if (a.ldd == 0) a.ldd = a.n;
     const bool bf16 = a.weights_dt == UZU_DT_BF16;

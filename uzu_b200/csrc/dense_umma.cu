@@ -249,11 +249,13 @@ bool dense_umma_applicable(const uzu_dense_linear_args& a) {
 }
 
 void encode_dense_umma(uzu_command_buffer* cmd, const uzu_dense_linear_args& a) {
-    const size_t quads = (size_t)a.m * a.k / 4;
-    launch(cmd, "dense_cast_bf16_kernel", dense_cast_bf16_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, (const float*)a.a, a.lda,
-           (__nv_bfloat16*)a.workspace, a.m, a.k, a.a_op);
+    if (!a.a_bf16) {
+        const size_t quads = (size_t)a.m * a.k / 4;
+        launch(cmd, "dense_cast_bf16_kernel", dense_cast_bf16_kernel, dim3((unsigned)((quads + 255) / 256)), dim3(256), 0, (const float*)a.a, a.lda,
+               (__nv_bfloat16*)a.workspace, a.m, a.k, a.a_op);
+    }
     DenseUmmaParams p{};
-    p.a = (const __nv_bfloat16*)a.workspace;
+    p.a = a.a_bf16 ? (const __nv_bfloat16*)a.a : (const __nv_bfloat16*)a.workspace;
     p.w = (const __nv_bfloat16*)a.w;
     p.d = (float*)a.d;
     p.gate = (const float*)a.gate;

@@ -342,6 +342,7 @@ struct GeneralDeltaLayer {   // generalized delta rule mixer: decay and removal 
 struct LatentAttentionLayer {   // latent attention: normed query latent, shared normed kv latent + one rotated key part
     DenseMatrix in;             // rows [query latent | kv latent | rotated key part | output gate]; a layer that borrows its cache has no kv rows
     DenseMatrix q_up, key_absorb /* heads x [rank, dim] = per-head key up-projection transposed */, value_up /* heads x [vdim, rank] */, out;
+    DenseMatrix kv_up;          // optional [heads * dim + heads * vdim, rank]: key rows then value rows, for prompt passes that expand the latents
     Buf q_norm, latent_norm;    // f32
     Buf sink;                   // f32 [heads] (optional): one more term exp(sink) in every softmax denominator
     uint32_t heads = 0, dim = 0, rot_dim = 0, vdim = 0, rank = 0, q_rank = 0;
@@ -547,6 +548,8 @@ struct uzu_engine {
         Buf route_scratch;                               // the experts a long pass picked, between the router's two launches
         Buf sub_out;                                     // a sublayer's result before its own norm (sandwich layers)
         Buf token_factors;                               // per (token, head) decay, gain, floor and normaliser product of a gated matrix memory
+        Buf expand_f32, expand_keys, expand_values;      // a prompt pass's expanded latents: f32 [rows, heads * (dim + vdim)], then bf16 keys and values
+        uint32_t expand_rows = 0;                        // rows the three hold
         bool redirect = false;                           // the sublayer being encoded writes sub_out instead of adding into resid
         // ... or, in short passes, its output projection's epilogue applies the sublayer's own norm, adds into resid and norms the
         // updated stream for the next reader (`reader`, optional) by itself: no launch between the projection and the next sublayer

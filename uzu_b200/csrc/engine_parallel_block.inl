@@ -790,7 +790,17 @@ static void load_vakesun_model(uzu_engine* e, const Json& cfg, const std::string
                         for (uint32_t r = 0; r < A.rank; ++r) t[((size_t)h * A.rank + r) * A.dim + d] = uk.v[((size_t)h * A.dim + d) * A.rank + r];
                 A.key_absorb = upload_matrix(e, t, A.rank, A.dim, A.heads);
             }
-            A.value_up = upload_matrix(e, read_floats(pl, p + "mix.uv", {A.heads * A.vdim, A.rank}).v, A.vdim, A.rank, A.heads);
+            {
+                HostTensor uv = read_floats(pl, p + "mix.uv", {A.heads * A.vdim, A.rank});
+                A.value_up = upload_matrix(e, uv.v, A.vdim, A.rank, A.heads);
+                // long prompt passes in bf16 expand the latents of their window into keys and values (one product on the tensor-memory kernel)
+                // and run the tensor-pipe softmax attention on them: a second copy of the two up-projections, stacked
+                if (e->store_dt == UZU_DT_BF16 && A.rank % 64 == 0 && A.dim % 16 == 0 && A.vdim % 16 == 0 && A.dim <= 128 && A.vdim <= 128) {
+                    std::vector<float> kv = read_floats(pl, p + "mix.uk", {A.heads * A.dim, A.rank}).v;
+                    kv.insert(kv.end(), uv.v.begin(), uv.v.end());
+                    A.kv_up = upload_matrix(e, kv, A.heads * (A.dim + A.vdim), A.rank);
+                }
+            }
             A.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
             A.q_norm = upload_f32(e, read_floats(pl, p + "mix.dq.norm", {A.q_rank}).v);
             A.sink = upload_f32(e, read_floats(pl, p + "mix.sink", {A.heads}).v);
@@ -843,7 +853,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     if (!e->parallel_block) return;
     const uint32_t W = e->model_dim;
     uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1, kmax = e->model_dim;
-    uint32_t proj2 = 1, tickets = 1, prompt_partial = 0, factor_heads = 0;
+    uint32_t proj2 = 1, tickets = 1, prompt_partial = 0, factor_heads = 0, expand_cols = 0, expand_rows = 0;
     bool second_norm = false, sandwich = false;
     for (const Layer& L : e->layers) {
         second_norm = second_norm || L.pre_mlp.present;
@@ -901,6 +911,10 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             gated = std::max(gated, A.heads * A.vdim);
             partial = std::max(partial, A.heads * (A.rank + 2));
             kmax = std::max({kmax, A.q_rank, A.heads * A.vdim});
+            if (A.kv_up.w.b) {      // rows a pass may expand: its own, the window before them (from a tile's edge), or the whole context without a window
+                expand_cols = std::max(expand_cols, A.kv_up.rows);
+                expand_rows = std::max(expand_rows, MAX_ROWS + (A.window ? A.window + 64 : e->max_context));
+            }
         }
         if (L.gmlp.kind == GatedMlp::RoutedExperts) proj2 = std::max(proj2, L.gmlp.router.rows);
         if (L.gmlp.unit == GatedMlp::ReluSquared) proj2 = std::max(proj2, L.gmlp.gate_up.rows);
@@ -920,6 +934,12 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     if (second_norm) P.normed2 = dev(R * W * 4);
     if (sandwich) P.sub_out = dev(R * W * 4);
     if (factor_heads) P.token_factors = dev(4 * R * factor_heads * 4);
+    if (expand_cols) {
+        P.expand_rows = std::min(expand_rows, 16384u);      // longer ranges take the kernel that reads the latents directly
+        P.expand_f32 = dev((size_t)P.expand_rows * expand_cols * 4);
+        P.expand_keys = dev((size_t)P.expand_rows * expand_cols * 2);
+        P.expand_values = dev((size_t)P.expand_rows * expand_cols * 2);
+    }
     P.proj2 = dev(R * proj2 * 4);
     P.pair_weight = dev(R * top * 4);
     P.pair_weight_compact = dev(R * top * 4);
@@ -1171,6 +1191,31 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
     if (q_norm_in_prepare) { pa.q_latent = P.proj.ptr(); pa.q_latent_scales = A.q_norm.ptr(); pa.q_latent_out = P.lat.ptr(); pa.q_rank = A.q_rank; pa.q_latent_stride = ld; }
     if (pa.kv || pa.q || pa.q_latent) uzu_latent_prepare_encode(cmd, &pa);
     if (q_norm_in_prepare) encode_dense(e, cmd, A.q_up, P.lat.ptr(), A.q_rank, m, P.wide.ptr());      // q [m, heads, dim]
+    // Long prompt passes over a bf16 cache: the latents of the visible range become keys and values per head again (one product on the
+    // tensor-memory kernel, A = the cache rows as they are), stored as bf16, and the tensor-pipe softmax attention runs on them with the
+    // sink and the head gate; its output is the heads' weighted value sums, so no value projection follows. The range starts at a key
+    // tile's edge (64) at or before the first visible row; the temporary rows are addressed by their absolute position.
+    if (A.kv_up.w.b && !pc.dynamic && m >= 64 && A.rot_dim == 0 && A.gate_per_head) {
+        const uint32_t first_seen = A.window && S.length + 1 > A.window ? S.length + 1 - A.window : 0u;
+        const uint32_t lo = first_seen / 64 * 64, rows = S.length + m - lo;
+        const uint32_t kn = A.heads * A.dim, vn = A.heads * A.vdim;
+        if (rows >= 128 && rows <= P.expand_rows && (S.keys & 15) == 0) {
+            uzu_dense_linear_args x = dense_args(e, A.kv_up, S.keys + (uint64_t)lo * A.rank * 2, rows, P.expand_f32.ptr());
+            x.a_bf16 = 1; x.lda = A.rank;
+            uzu_dense_linear_encode(cmd, &x);
+            uzu_rows_to_bf16_encode(cmd, P.expand_f32.ptr(), kn + vn, P.expand_keys.ptr(), rows, kn);
+            uzu_rows_to_bf16_encode(cmd, P.expand_f32.ptr() + (uint64_t)kn * 4, kn + vn, P.expand_values.ptr(), rows, vn);
+            uzu_window_attention_args wa{};
+            wa.query = P.wide.ptr(); wa.out = P.gated_mix.ptr();
+            wa.keys = P.expand_keys.ptr() - (uint64_t)lo * kn * 2; wa.values = P.expand_values.ptr() - (uint64_t)lo * vn * 2;     // row j of the cache is row j - lo here
+            wa.rows = m; wa.heads = A.heads; wa.kv_heads = A.heads; wa.dim = A.dim; wa.vdim = A.vdim; wa.prefix = S.length; wa.cache_dt = UZU_DT_BF16;
+            wa.window = A.window; wa.scale = A.scale; wa.splits = 1;
+            wa.sinks = A.sink.ptr(); wa.head_gate = P.proj.ptr() + (uint64_t)A.gate_offset * 4; wa.head_gate_stride = ld;
+            uzu_window_attention_encode(cmd, &wa);
+            encode_into_residual(e, cmd, A.out, P.gated_mix.ptr(), vn, m);
+            return;
+        }
+    }
     if (A.dim) {   // absorbed key projection, one z per head: query[:, h, 0:rank] = q[:, h, 0:dim] . (W_uk^h as [rank, dim])^T
         uzu_dense_linear_args x = dense_args(e, A.key_absorb, P.wide.ptr(), m, P.query.ptr());
         x.lda = A.heads * qd; x.ldd = A.heads * width; x.batch = A.heads;

@@ -176,6 +176,15 @@ __global__ void embedding_f32_kernel(const uint32_t* tokens, const TW* table, fl
     out[(size_t)row * n + i] = v * scale;
 }
 
+__global__ void rows_to_bf16_kernel(const float* src, uint32_t src_stride, __nv_bfloat16* dst, uint32_t rows, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * n) return;
+    const size_t r = idx / n, c = idx % n;
+    dst[idx] = __float2bfloat16_rn(src[r * src_stride + c]);
+}
+
 __global__ void clamped_glu_kernel(const float* gate_up, float* out, uint32_t rows, uint32_t f, float limit, float alpha) {
     pdl_launch_dependents();
     pdl_wait();
@@ -479,6 +488,15 @@ void uzu_norm_add_encode(uzu_command_buffer* cmd, const uzu_norm_add_args* a) {
         launch(cmd, "norm_add_elementwise_kernel", norm_add_elementwise_kernel, dim3((b.n + 255) / 256, b.rows), dim3(256), 0, b);
     else
         launch(cmd, "norm_add_kernel", norm_add_kernel, dim3(b.rows), dim3(256), 0, b);
+}
+
+void uzu_rows_to_bf16_encode(uzu_command_buffer* cmd, uint64_t src, uint32_t src_stride, uint64_t dst, uint32_t rows, uint32_t n) {
+    if (!encodable(cmd, "rows_to_bf16") || rows == 0 || n == 0) return;
+    if (!src || !dst || src_stride < n) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "rows_to_bf16: null operand or a row stride below the row size");
+        return;
+    }
+    launch(cmd, "rows_to_bf16_kernel", rows_to_bf16_kernel, dim3(blocks256((size_t)rows * n)), dim3(256), 0, (const float*)src, src_stride, (__nv_bfloat16*)dst, rows, n);
 }
 
 void uzu_token_gate_encode(uzu_command_buffer* cmd, const uzu_token_gate_args* a) {

@@ -254,12 +254,16 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attention_kernel(const u
         cta_l = fmaf(warp_l[wq], wf[wq], cta_l);
     }
     float* result = wa_smem + WA_WARPS * a.vdim;     // [vdim]
+    // a sink adds exp(sink - max) to the denominator; a head gate multiplies the head's result by its sigmoid
+    const float sink = a.sinks ? reinterpret_cast<const float*>(a.sinks)[h] : -INFINITY;
+    const float gate = a.head_gate ? 1.0f / (1.0f + expf(-reinterpret_cast<const float*>(a.head_gate)[(size_t)t * a.head_gate_stride + h])) : 1.0f;
     if (splits == 1) {
+        const float norm = gate / (a.sinks ? cta_l + expf(sink - cta_m) : cta_l);
         for (uint32_t c = tid; c < a.vdim; c += blockDim.x) {
             float v = 0.0f;
 #pragma unroll
             for (int wq = 0; wq < WA_WARPS; ++wq) v = fmaf(wa_smem[wq * a.vdim + c], wf[wq], v);
-            result[c] = v / cta_l;
+            result[c] = v * norm;
         }
     } else {
         const uint32_t pw = a.vdim + 2;
@@ -291,6 +295,8 @@ __global__ void __launch_bounds__(WA_WARPS * 32) window_attention_kernel(const u
         __syncthreads();
         float all_l = 0.0f;
         for (uint32_t sp = 0; sp < splits; ++sp) all_l = fmaf(split_l[sp], split_f[sp], all_l);      // in split order
+        if (a.sinks) all_l += expf(sink - all_m);
+        all_l /= gate;
         for (uint32_t c = tid; c < a.vdim; c += blockDim.x) {
             float v = 0.0f;
             uint32_t sp = 0;

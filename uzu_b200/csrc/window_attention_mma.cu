@@ -251,7 +251,11 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(const uzu_win
         float l = run_l[r];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (a.sinks) l += exp2f(reinterpret_cast<const float*>(a.sinks)[h] * kLog2e - run_m[r]);      // the sink's term (the maximum is in units of ln 2)
         inv_l[r] = 1.0f / l;
+        const uint32_t row = row_lo + 8 * r;
+        if (a.head_gate && row < rows_here)
+            inv_l[r] *= 1.0f / (1.0f + expf(-reinterpret_cast<const float*>(a.head_gate)[(size_t)(m0 + row) * a.head_gate_stride + h]));
     }
     const size_t row_stride = (size_t)a.heads * vdim;
     float* out = reinterpret_cast<float*>(a.out) + (size_t)m0 * row_stride + (size_t)h * vdim;
